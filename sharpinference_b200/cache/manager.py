@@ -11,13 +11,14 @@ Here:
 
 * Every schedule entry whose mixer declares a :class:`CacheSpec` writes into a *group*: the
   entries with equal specs.  A group owns one device tensor
-  ``[entries, pages, 2 (K|V), kv_heads, page_size, head_dim]`` and one free list of page ids; a
+  ``[entries, pages, planes (K|V, or keys only), kv_heads, page_size, head_dim]`` and one free list of page ids; a
   page id addresses the same page in every entry of the group, so a request has one block table
   per group (``table[logical_block] -> page id``, -1 where nothing is held).
 * Pages are taken when a step is about to write positions (``reserve``: all or nothing for the
   whole step), and given back (a) when the request ends (``free_request``), (b) after a step, for
   groups whose mask forgets the past (chunk, window): every page that lies wholly below the
-  lowest position a later query can see (``commit``).  A freed page is handed out again at once.
+  lowest position a later query can see (``commit``), except the pages that hold the first positions a window
+  keeps visible (``CacheSpec.keep_first``).  A freed page is handed out again at once.
 * Every live request holds one *state slot*: an index into per-entry tensors
   ``[slots, *StateSpec.shape]`` for mixers that keep state of fixed size.  The slot is assigned
   (and its state zeroed) at ``add_request`` and returned at ``free_request``, whether or not any
@@ -90,7 +91,7 @@ class CacheGroup:
     spec: CacheSpec
     entries: List[int]                  # schedule indices that WRITE into this group, in order
     pages: FreeList
-    kv: Optional[torch.Tensor] = None   # [len(entries), num_pages, 2, kv_heads, page_size, head_dim]
+    kv: Optional[torch.Tensor] = None   # [len(entries), num_pages, planes, kv_heads, page_size, head_dim]
 
     def lowest_needed(self, next_pos: int) -> int:
         """The lowest position that a query at ``next_pos`` or later can still read."""
@@ -169,7 +170,7 @@ class CacheManager:
         if allocate:
             for g in self.groups:
                 s = g.spec
-                g.kv = torch.zeros((len(g.entries), g.pages.capacity, 2, s.num_kv_heads, page_size, s.head_dim),
+                g.kv = torch.zeros((len(g.entries), g.pages.capacity, s.planes, s.num_kv_heads, page_size, s.head_dim),
                                    dtype=dtype, device=self.device)
             for index, sspec in self._entry_state_spec.items():
                 self._entry_state[index] = torch.zeros((max_requests, *sspec.shape), dtype=sspec.dtype,
@@ -302,7 +303,8 @@ class CacheManager:
             lo = g.lowest_needed(rc.length)
             table = rc.tables[g.index]
             upto = min(lo // self.page_size, len(table))
-            for b in range(rc.released.get(g.index, 0), upto):       # what lies below was given back before
+            kept = (g.spec.keep_first + self.page_size - 1) // self.page_size    # blocks with positions that stay visible
+            for b in range(max(rc.released.get(g.index, 0), kept), upto):        # what lies below was given back before
                 if table[b] >= 0:
                     g.pages.give_back(table[b])
                     table[b] = -1

@@ -40,11 +40,11 @@ def pages_per_group(groups: Sequence[Tuple[object, int]], *, budget_bytes: int, 
     def up(n: int) -> int:
         return (n + page_size - 1) // page_size * page_size
 
-    per_token = [2 * spec.num_kv_heads * spec.head_dim * itemsize * entries for spec, entries in groups]
+    per_token = [getattr(spec, "planes", 2) * spec.num_kv_heads * spec.head_dim * itemsize * entries for spec, entries in groups]
     bounded = [spec.kind != "full" for spec, _ in groups]
     # what a forgetting group can hold at most: per request its span, the portion in flight and the page that
     # straddles the edge
-    cap = [min(MAX_GROUP_TOKENS, max_batch * (up(spec.span) + up(max_tokens_per_step) + page_size)) if b else 0
+    cap = [min(MAX_GROUP_TOKENS, max_batch * (up(spec.span) + up(getattr(spec, "keep_first", 0)) + up(max_tokens_per_step) + page_size)) if b else 0
            for (spec, _), b in zip(groups, bounded)]
     tokens = [0] * len(groups)
     full = [i for i, b in enumerate(bounded) if not b]

@@ -13,6 +13,13 @@
 //
 // The tiles start at the row's lowest visible position, which depends on the row's own
 // position only, so a row's result does not depend on how the step was cut or batched.
+//
+// Three further rules, each off by default.  `kv_planes` = 1: a page holds keys only and a value is the
+// key row itself (its leading `d` elements): attention whose values are its keys, or keys and values that are
+// two readings of one cached latent.  `keep_first` > 0 (window mask): the first `keep_first` positions of a
+// sequence stay visible beyond the window; the walk then runs over the kept positions below the window first and
+// the window after them.  `dist_bias` [far + 1, nq]: a number added to the scaled score by the distance
+// pos - key (distances beyond `far` read row `far`).
 #include "common.cuh"
 
 constexpr int ATT_THREADS = 128;
@@ -29,6 +36,10 @@ struct PagedAttnArgs {
     int T, nq, nkv, d, max_blocks, page_size;
     int mask_kind, mask_span;
     float scale;
+    int kv_planes;           // 2: [K|V] planes a page; 1: keys only, values are the keys
+    int keep_first;          // window mask: positions below this stay visible
+    const float* dist_bias;  // [dist_far + 1, nq] or null
+    int dist_far;
 };
 
 template <typename TS>
@@ -46,7 +57,11 @@ __global__ void paged_attention_generic_kernel(PagedAttnArgs a) {
     const int lo = visible_lo(pos, a.mask_kind, a.mask_span);
     const int* table = a.block_table + (size_t)a.row_req[t] * a.max_blocks;
     const size_t plane = (size_t)a.nkv * a.page_size * d;
+    const size_t vplane = a.kv_planes == 2 ? plane : 0;
     const TS* kv = (const TS*)a.kv_base;
+    // kept positions below the window come first in the walk, the window behind them
+    const int n_first = (a.mask_kind == SHARPI_MASK_WINDOW && a.keep_first > 0) ? min(a.keep_first, lo) : 0;
+    const int n_keys_all = n_first + pos - lo + 1;
 
     const TS* qrow = (const TS*)a.q + ((size_t)t * a.nq + h) * d;
     for (int i = threadIdx.x; i < d; i += ATT_THREADS) q_s[i] = to_float(qrow[i]);
@@ -58,18 +73,20 @@ __global__ void paged_attention_generic_kernel(PagedAttnArgs a) {
     for (int r = 0; r < DPT; ++r) acc[r] = 0.0f;
     float m_run = -INFINITY, l_run = 0.0f;
 
-    for (int tile = lo; tile <= pos; tile += ATT_TILE) {
-        const int key = tile + threadIdx.x;
+    for (int tile = 0; tile < n_keys_all; tile += ATT_TILE) {
+        const int at = tile + threadIdx.x;
+        const int key = at < n_first ? at : lo + (at - n_first);
         float s = -INFINITY;
         long long off = -1;
-        if (key <= pos) {
+        if (at < n_keys_all) {
             const int page = table[key / a.page_size];
             if (page >= 0) {
-                off = (long long)page * 2 * plane + ((long long)kvh * a.page_size + key % a.page_size) * d;
+                off = (long long)page * a.kv_planes * plane + ((long long)kvh * a.page_size + key % a.page_size) * d;
                 const TS* krow = kv + off;
                 float dot = 0.0f;
                 for (int i = 0; i < d; ++i) dot += q_s[i] * to_float(krow[i]);
                 s = dot * a.scale;
+                if (a.dist_bias) s += a.dist_bias[(size_t)min(pos - key, a.dist_far) * a.nq + h];
             }
         }
         const float m_tile = block_max(s, scratch);
@@ -83,7 +100,7 @@ __global__ void paged_attention_generic_kernel(PagedAttnArgs a) {
         const float l_tile = block_sum(p, scratch);  // has __syncthreads inside: p_s/off_s are visible after it
         l_run = l_run * corr + l_tile;
         m_run = m_new;
-        const int n_keys = min(ATT_TILE, pos - tile + 1);
+        const int n_keys = min(ATT_TILE, n_keys_all - tile);
 #pragma unroll
         for (int r = 0; r < DPT; ++r) {
             const int i = threadIdx.x + r * ATT_THREADS;
@@ -91,7 +108,7 @@ __global__ void paged_attention_generic_kernel(PagedAttnArgs a) {
                 float sum = 0.0f;
                 for (int k = 0; k < n_keys; ++k) {
                     const long long o = off_s[k];
-                    if (o >= 0) sum += p_s[k] * to_float(kv[o + plane + i]);
+                    if (o >= 0) sum += p_s[k] * to_float(kv[o + vplane + i]);
                 }
                 acc[r] = acc[r] * corr + sum;
             }
@@ -109,13 +126,17 @@ __global__ void paged_attention_generic_kernel(PagedAttnArgs a) {
 SHARPI_API int sharpi_paged_attention_generic(const void* q, const void* kv_base, const int* block_table,
                                               const int* row_req, const int* positions, void* out, int dtype,
                                               int T, int nq, int nkv, int d, int max_blocks, int page_size,
-                                              int mask_kind, int mask_span, float scale, cudaStream_t stream) {
+                                              int mask_kind, int mask_span, float scale, int kv_planes,
+                                              int keep_first, const float* dist_bias, int dist_far,
+                                              cudaStream_t stream) {
     if (T <= 0) return SHARPI_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || d > ATT_MAX_D || nq > 65535 || page_size <= 0 ||
         max_blocks <= 0)
         return SHARPI_BAD_ARGUMENT;
     if (mask_kind != SHARPI_MASK_FULL && mask_span <= 0) return SHARPI_BAD_ARGUMENT;
+    if ((kv_planes != 1 && kv_planes != 2) || keep_first < 0 || (dist_bias && dist_far < 0)) return SHARPI_BAD_ARGUMENT;
     PagedAttnArgs a;
+    a.kv_planes = kv_planes; a.keep_first = keep_first; a.dist_bias = dist_bias; a.dist_far = dist_far;
     a.q = q; a.kv_base = kv_base; a.block_table = block_table; a.row_req = row_req; a.positions = positions;
     a.out = out; a.T = T; a.nq = nq; a.nkv = nkv; a.d = d; a.max_blocks = max_blocks; a.page_size = page_size;
     a.mask_kind = mask_kind; a.mask_span = mask_span; a.scale = scale;

@@ -469,3 +469,78 @@ SHARPI_API int sharpi_scale(float* y, float s, long long n, cudaStream_t stream)
     SHARPI_LAUNCH_PDL(scale_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, y, s, n);
     return SHARPI_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// Residual add fused with the element-wise squashing norm ("dynamic tanh"):
+//   x += delta (in place unless `rows` gathers);  out = tanh(alpha * x) * w + b
+// with one scalar alpha (read from device memory, so that a captured graph holds no copy of it), a weight and a
+// bias vector.  No statistic of the row is formed, so every element stands alone: four elements a thread, rows
+// in grid.y.  Same interface as sharpi_add_rmsnorm (optional unrounded float32 copy).
+// ---------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void __launch_bounds__(256)
+add_dyt_kernel(float* x, const float* __restrict__ delta, const float* __restrict__ w, const float* __restrict__ b,
+               const float* __restrict__ alpha, const int* __restrict__ rows, int H, TO* __restrict__ out,
+               float* __restrict__ out32) {
+    pdl_wait();
+    const int t = blockIdx.y;
+    const size_t src = (size_t)(rows ? rows[t] : t) * H;
+    const float al = alpha[0];
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < H; i += gridDim.x * blockDim.x) {
+        float v = x[src + i];
+        if (delta) {
+            v += delta[src + i];
+            if (!rows) x[src + i] = v;
+        }
+        const float y = tanhf(al * v) * w[i] + (b ? b[i] : 0.0f);
+        out[(size_t)t * H + i] = from_float<TO>(y);
+        if (out32) out32[(size_t)t * H + i] = y;
+    }
+}
+
+SHARPI_API int sharpi_add_dyt(float* x, const float* delta, const float* w, const float* b, const float* alpha,
+                              const int* rows, int T, int H, void* out, int out_dtype, float* out32,
+                              cudaStream_t stream) {
+    if (T <= 0) return SHARPI_OK;
+    if (H <= 0 || T > 65535 * 1024 || !w || !alpha) return SHARPI_BAD_ARGUMENT;
+    // rows in grid.y are limited to 65535: larger steps walk them in slices
+    for (int t0 = 0; t0 < T; t0 += 65535) {
+        const int n = T - t0 < 65535 ? T - t0 : 65535;
+        const dim3 grid((H + 1023) / 1024 > 0 ? (H + 1023) / 1024 : 1, n);
+        float* xs = rows ? x : x + (size_t)t0 * H;
+        const float* ds = delta ? (rows ? delta : delta + (size_t)t0 * H) : nullptr;
+        const int* rs = rows ? rows + t0 : nullptr;
+        float* o32 = out32 ? out32 + (size_t)t0 * H : nullptr;
+        if (out_dtype == SHARPI_F32)
+            SHARPI_LAUNCH_PDL(add_dyt_kernel<float>, grid, 256, 0, stream, xs, ds, w, b, alpha, rs, H,
+                              (float*)out + (size_t)t0 * H, o32);
+        else if (out_dtype == SHARPI_BF16)
+            SHARPI_LAUNCH_PDL(add_dyt_kernel<bf16>, grid, 256, 0, stream, xs, ds, w, b, alpha, rs, H,
+                              (bf16*)out + (size_t)t0 * H, o32);
+        else
+            return SHARPI_BAD_ARGUMENT;
+    }
+    return SHARPI_OK;
+}
+
+// out = o * sigmoid(g): a gate on the concatenated heads of a mixer, `o` in the activation dtype (the attention
+// kernels' output), `g` the float32 product of the gate's projection; the sigmoid and the product are float32.
+template <typename TO>
+__global__ void __launch_bounds__(256) sigmoid_gate_kernel(const TO* o, const float* g, TO* out, long long n) {
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_float<TO>(to_float(o[i]) / (1.0f + expf(-g[i])));
+}
+
+SHARPI_API int sharpi_sigmoid_gate(const void* o, const float* g, void* out, int dtype, long long n,
+                                   cudaStream_t stream) {
+    if (n <= 0) return SHARPI_OK;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == SHARPI_F32)
+        SHARPI_LAUNCH_PDL(sigmoid_gate_kernel<float>, blocks, 256, 0, stream, (const float*)o, g, (float*)out, n);
+    else if (dtype == SHARPI_BF16)
+        SHARPI_LAUNCH_PDL(sigmoid_gate_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)o, g, (bf16*)out, n);
+    else
+        return SHARPI_BAD_ARGUMENT;
+    return SHARPI_OK;
+}

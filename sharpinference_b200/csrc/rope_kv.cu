@@ -39,13 +39,14 @@ struct QkvPostArgs {
     float temp_attn_scale;   // temperature factor on q; floor_scale <= 0: none
     float temp_floor_scale;
     int write_kv;            // 0: this layer reads a cache that another layer writes
+    int kv_planes;           // 2: q|k|v come in and a page holds [K|V]; 1: q|k come in and a page holds keys only
 };
 
 template <typename TO>
 __global__ void qkv_post_kernel(QkvPostArgs a) {
     const int warps_per_block = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int slots = a.nq + 2 * a.nkv;
+    const int slots = a.nq + a.kv_planes * a.nkv;
     const long long work = (long long)blockIdx.x * warps_per_block + warp;
     if (work >= (long long)a.T * slots) return;
     const int t = (int)(work / slots);
@@ -67,7 +68,7 @@ __global__ void qkv_post_kernel(QkvPostArgs a) {
         const int page = a.block_table[(size_t)a.row_req[t] * a.max_blocks + pos / a.page_size];
         if (page < 0) return;  // the host checks before the launch that every written position has a page
         const size_t plane = (size_t)a.nkv * a.page_size * d;
-        dst = (TO*)a.kv_base + ((size_t)page * 2 + (is_k ? 0 : 1)) * plane +
+        dst = (TO*)a.kv_base + ((size_t)page * a.kv_planes + (is_k ? 0 : 1)) * plane +
               ((size_t)head * a.page_size + (pos % a.page_size)) * d;
     }
 
@@ -151,7 +152,7 @@ __global__ void __launch_bounds__(256) qkv_post_vec_kernel(QkvPostArgs a) {
     pdl_wait();
     const int warps_per_block = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int slots = a.nq + 2 * a.nkv;
+    const int slots = a.nq + a.kv_planes * a.nkv;
     const int groups = (slots + QKV_SLOTS - 1) / QKV_SLOTS;
     const long long work = (long long)blockIdx.x * warps_per_block + warp;
     if (work >= (long long)a.T * groups) return;
@@ -205,7 +206,7 @@ __global__ void __launch_bounds__(256) qkv_post_vec_kernel(QkvPostArgs a) {
         } else {
             if (page < 0) continue;      // no cache write for this layer (the host checks that written positions have pages)
             const int head = is_k ? slot - a.nq : slot - a.nq - a.nkv;
-            dst = (TO*)a.kv_base + ((size_t)page * 2 + (is_k ? 0 : 1)) * plane +
+            dst = (TO*)a.kv_base + ((size_t)page * a.kv_planes + (is_k ? 0 : 1)) * plane +
                   ((size_t)head * a.page_size + (pos % a.page_size)) * d;
         }
         float scale = 1.0f;
@@ -243,7 +244,7 @@ SHARPI_API int sharpi_qkv_post(const float* qkv, const int* positions, const int
                                const float* inv_freq, void* q_out, void* kv_base, int out_dtype, int T, int nq,
                                int nkv, int d, int max_blocks, int page_size, int pairing, float l2_eps,
                                float temp_attn_scale, float temp_floor_scale, int write_kv, int l2_count,
-                               cudaStream_t stream) {
+                               int kv_planes, cudaStream_t stream) {
     if (T <= 0) return SHARPI_OK;
     if (nq <= 0 || nkv <= 0 || d <= 0 || (d & 1) || d > 512 || page_size <= 0 || max_blocks <= 0)
         return SHARPI_BAD_ARGUMENT;
@@ -255,9 +256,11 @@ SHARPI_API int sharpi_qkv_post(const float* qkv, const int* positions, const int
     a.pairing = inv_freq ? pairing : ROPE_NONE; a.l2_eps = l2_eps;
     a.l2_count = (l2_count > 0 && l2_count <= d) ? l2_count : d;
     a.temp_attn_scale = temp_attn_scale; a.temp_floor_scale = temp_floor_scale; a.write_kv = write_kv;
+    if (kv_planes != 1 && kv_planes != 2) return SHARPI_BAD_ARGUMENT;
+    a.kv_planes = kv_planes;
     if (out_dtype != SHARPI_F32 && out_dtype != SHARPI_BF16) return SHARPI_BAD_ARGUMENT;
-    const long long work = (long long)T * (nq + 2 * nkv);
-    const long long vec_work = (long long)T * ((nq + 2 * nkv + QKV_SLOTS - 1) / QKV_SLOTS);
+    const long long work = (long long)T * (nq + kv_planes * nkv);
+    const long long vec_work = (long long)T * ((nq + kv_planes * nkv + QKV_SLOTS - 1) / QKV_SLOTS);
     const uintptr_t ptrs = reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
                            reinterpret_cast<uintptr_t>(kv_base) | reinterpret_cast<uintptr_t>(inv_freq);
     if (d % 4 == 0 && a.pairing != ROPE_HALVES && (ptrs & 15) == 0) {

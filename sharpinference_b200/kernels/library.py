@@ -33,8 +33,8 @@ SIGNATURES: Dict[str, Tuple[str, list]] = {
     "sharpi_swiglu": ("elementwise", [P, P, P, P, I, I, I, P]),
     "sharpi_add": ("elementwise", [P, P, P, LL, P]),
     "sharpi_timestamp": ("elementwise", [P, I, P]),
-    "sharpi_qkv_post": ("rope_kv", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, I, I, P]),
-    "sharpi_paged_attention_generic": ("attention_generic", [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P]),
+    "sharpi_qkv_post": ("rope_kv", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, I, I, I, P]),
+    "sharpi_paged_attention_generic": ("attention_generic", [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P, I, P]),
     "sharpi_attention_decode": ("attention_decode", [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P]),
     "sharpi_attention_prefill": ("attention_prefill", [P, P, P, P, P, I, I, I, I, I, I, I, I, F, P]),
     "sharpi_attention_prefill_tc": ("attention_prefill_tc", [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P]),
@@ -73,6 +73,14 @@ SIGNATURES: Dict[str, Tuple[str, list]] = {
     "sharpi_gated_act": ("elementwise", [P, P, I, I, I, I, P]),
     "sharpi_tanh": ("elementwise", [P, P, I, LL, P]),
     "sharpi_scale": ("elementwise", [P, F, LL, P]),
+    "sharpi_sigmoid_gate": ("elementwise", [P, P, P, I, LL, P]),
+    "sharpi_add_dyt": ("elementwise", [P, P, P, P, P, P, I, I, P, I, P, P]),
+    "sharpi_latent_down_post": ("latent", [P, I, I, I, I, I, P, P, F, P, P, P, I, I, P, P, P, I, I, I, I, I, P]),
+    "sharpi_head_major": ("latent", [P, I, I, I, I, I, I, P, I, P]),
+    "sharpi_head_minor": ("latent", [P, I, I, I, I, I, P, I, P]),
+    "sharpi_latent_q_join": ("latent", [P, P, P, P, I, I, I, I, I, I, I, P, I, P]),
+    "sharpi_ssd_scan": ("mamba2", [P, I, I, I, I, P, I, I, P, P, P, P, P, P, LL, P, I, I, I, I, I, I, P]),
+    "sharpi_gated_group_norm": ("mamba2", [P, P, I, P, F, I, I, I, P, I, P]),
 }
 
 _libs: Dict[str, ctypes.CDLL] = {}

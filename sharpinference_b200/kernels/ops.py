@@ -171,13 +171,14 @@ def concat2(a: torch.Tensor, delta: Optional[torch.Tensor], b: torch.Tensor, out
 def qkv_post(qkv: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor, block_table: torch.Tensor,
              inv_freq: Optional[torch.Tensor], q_out: torch.Tensor, kv_layer: torch.Tensor, *, nq: int, nkv: int,
              d: int, page_size: int, pairing: int, l2_eps: float, temp_attn_scale: float, temp_floor_scale: float,
-             write_kv: bool, l2_count: int = 0) -> None:
+             write_kv: bool, l2_count: int = 0, kv_planes: int = 2) -> None:
     """RoPE, per-head L2 norm, temperature factor, q store and K/V scatter into pages.
 
     ``qkv`` fp32 [T, (nq + 2 nkv) d]; ``kv_layer`` is one layer's pages
     ``[pages, 2, nkv, page_size, d]`` in the dtype of ``q_out``; ``l2_eps < 0`` and
     ``temp_floor_scale <= 0`` switch the norm and the temperature factor off.  ``l2_count`` (default ``d``) is the
     number of elements the norm's mean of squares divides by: fewer than ``d`` when the heads are padded with zeros.
+    ``kv_planes=1``: the values are the keys; ``qkv`` is [T, (nq + nkv) d] and a page holds keys only.
     """
     _need(qkv, "qkv", torch.float32)
     _need(positions, "positions", torch.int32)
@@ -186,10 +187,11 @@ def qkv_post(qkv: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor, 
     _need(q_out, "q_out")
     _need(kv_layer, "kv_layer", q_out.dtype)
     T = positions.numel()
-    if qkv.shape != (T, (nq + 2 * nkv) * d):
-        raise KernelError(f"qkv shape {tuple(qkv.shape)} is not [T={T}, (nq + 2 nkv) d = {(nq + 2 * nkv) * d}]")
-    if tuple(kv_layer.shape[1:]) != (2, nkv, page_size, d):
-        raise KernelError(f"kv_layer shape {tuple(kv_layer.shape)} is not [pages, 2, {nkv}, {page_size}, {d}]")
+    if qkv.shape != (T, (nq + kv_planes * nkv) * d):
+        raise KernelError(f"qkv shape {tuple(qkv.shape)} is not [T={T}, (nq + {kv_planes} nkv) d = "
+                          f"{(nq + kv_planes * nkv) * d}]")
+    if tuple(kv_layer.shape[1:]) != (kv_planes, nkv, page_size, d):
+        raise KernelError(f"kv_layer shape {tuple(kv_layer.shape)} is not [pages, {kv_planes}, {nkv}, {page_size}, {d}]")
     if inv_freq is not None:
         _need(inv_freq, "inv_freq", torch.float32)
         if inv_freq.numel() != d // 2:
@@ -198,14 +200,18 @@ def qkv_post(qkv: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor, 
                                     block_table.data_ptr(), _ptr(inv_freq), q_out.data_ptr(), kv_layer.data_ptr(),
                                     dtype_code(q_out.dtype), T, nq, nkv, d, block_table.shape[-1], page_size,
                                     pairing, float(l2_eps), float(temp_attn_scale), float(temp_floor_scale),
-                                    int(write_kv), int(l2_count), _stream()), "sharpi_qkv_post")
+                                    int(write_kv), int(l2_count), int(kv_planes), _stream()), "sharpi_qkv_post")
 
 
 def paged_attention_generic(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor,
                             row_req: torch.Tensor, positions: torch.Tensor, *, nq: int, nkv: int, d: int,
                             page_size: int, mask_kind: int, mask_span: int, scale: float,
-                            out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Attention of every row over the keys it may see in its request's pages; [T, nq d]."""
+                            out: Optional[torch.Tensor] = None, keep_first: int = 0,
+                            dist_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of every row over the keys it may see in its request's pages; [T, nq d].  A ``kv_layer`` with one
+    plane (``[pages, 1, nkv, page_size, d]``) holds keys only and the values are the keys.  ``keep_first``: under
+    a window mask the first positions of a sequence stay visible.  ``dist_bias`` float32 ``[far + 1, nq]`` is added
+    to the scaled score by the distance between query and key (distances beyond ``far`` read the last row)."""
     _need(q, "q")
     _need(kv_layer, "kv_layer", q.dtype)
     _need(block_table, "block_table", torch.int32)
@@ -214,10 +220,16 @@ def paged_attention_generic(q: torch.Tensor, kv_layer: torch.Tensor, block_table
     T = positions.numel()
     if out is None:
         out = torch.empty((T, nq * d), dtype=q.dtype, device=q.device)
+    if dist_bias is not None:
+        _need(dist_bias, "dist_bias", torch.float32)
+        if dist_bias.dim() != 2 or dist_bias.shape[1] != nq or dist_bias.shape[0] < 1:
+            raise KernelError(f"dist_bias is {tuple(dist_bias.shape)}, expected [far + 1, {nq}]")
     check(kernel("sharpi_paged_attention_generic")(q.data_ptr(), kv_layer.data_ptr(), block_table.data_ptr(),
                                                    row_req.data_ptr(), positions.data_ptr(), out.data_ptr(),
                                                    dtype_code(q.dtype), T, nq, nkv, d, block_table.shape[-1],
-                                                   page_size, mask_kind, mask_span, float(scale), _stream()),
+                                                   page_size, mask_kind, mask_span, float(scale),
+                                                   int(kv_layer.shape[1]), int(keep_first), _ptr(dist_bias),
+                                                   0 if dist_bias is None else dist_bias.shape[0] - 1, _stream()),
           "sharpi_paged_attention_generic")
     return out
 
@@ -1144,3 +1156,159 @@ def scale_(y: torch.Tensor, s: float) -> torch.Tensor:
     _need(y, "y", torch.float32)
     check(kernel("sharpi_scale")(y.data_ptr(), float(s), y.numel(), _stream()), "sharpi_scale")
     return y
+
+
+# ---------------------------------------------------------------------------------------
+# the element-wise squashing norm, latent attention, the state-space-duality scan
+# ---------------------------------------------------------------------------------------
+def add_dyt(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, bias: Optional[torch.Tensor],
+            alpha: torch.Tensor, out_dtype: torch.dtype, *, rows: Optional[torch.Tensor] = None,
+            want_fp32: bool = False):
+    """Residual add fused with ``tanh(alpha x) w + b`` (``alpha`` a float32 tensor of one element).  The interface of
+    :func:`add_rmsnorm`: without ``rows`` ``x += delta`` in place, with ``rows`` the gathered rows and ``x`` stays.
+    Returns ``(out, out32)``."""
+    _need(x, "x", torch.float32)
+    _need(weight, "weight", torch.float32)
+    _need(alpha, "alpha", torch.float32)
+    H = x.shape[-1]
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    if weight.numel() != H or (bias is not None and bias.numel() != H) or alpha.numel() != 1:
+        raise KernelError(f"weight, bias or alpha disagree with the width {H}")
+    if delta is not None:
+        _need(delta, "delta", torch.float32)
+        if delta.shape != x.shape:
+            raise KernelError(f"delta shape {tuple(delta.shape)} differs from x shape {tuple(x.shape)}")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        T = rows.numel()
+    else:
+        T = x.numel() // H
+    out = torch.empty((T, H), dtype=out_dtype, device=x.device)
+    out32 = None
+    if want_fp32:
+        out32 = out if out_dtype == torch.float32 else torch.empty((T, H), dtype=torch.float32, device=x.device)
+    alias = out32 is not None and out32.data_ptr() == out.data_ptr()
+    check(kernel("sharpi_add_dyt")(x.data_ptr(), _ptr(delta), weight.data_ptr(), _ptr(bias), alpha.data_ptr(), _ptr(rows),
+                                   T, H, out.data_ptr(), dtype_code(out_dtype), None if alias else _ptr(out32), _stream()),
+          "sharpi_add_dyt")
+    return out, out32
+
+
+def latent_down_post(down: torch.Tensor, *, q_rank: int, rank: int, rot: int, rot_dims: int,
+                     q_norm_weight: Optional[torch.Tensor], c_norm_weight: torch.Tensor, eps: float,
+                     positions: torch.Tensor, row_req: torch.Tensor, block_table: torch.Tensor,
+                     inv_freq: Optional[torch.Tensor], kv_layer: torch.Tensor, page_size: int,
+                     write_kv: bool = True) -> torch.Tensor:
+    """Behind the fused down projection ``down`` float32 ``[T, q_rank + rank + rot]`` of latent attention: the normed
+    query latent ``[T, q_rank]`` in the cache's dtype (returned), and ``[c | k_rot | 0]`` written into every row's
+    place in ``kv_layer [pages, planes, 1, page_size, D]`` (``[c | 0]`` into the value plane when there are two)."""
+    _need(down, "down", torch.float32)
+    _need(c_norm_weight, "c_norm_weight", torch.float32)
+    _need(kv_layer, "kv_layer")
+    T, ld = down.shape
+    planes, D = int(kv_layer.shape[1]), int(kv_layer.shape[-1])
+    if tuple(kv_layer.shape[1:]) != (planes, 1, page_size, D) or ld != q_rank + rank + rot:
+        raise KernelError(f"kv_layer {tuple(kv_layer.shape)} or the projection's width {ld} disagree with the sizes")
+    if inv_freq is not None:
+        _need(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() != rot_dims // 2:
+            raise KernelError(f"{rot_dims} rotated elements need {rot_dims // 2} frequencies, found {inv_freq.numel()}")
+    cq = torch.empty((T, q_rank), dtype=kv_layer.dtype, device=down.device)
+    check(kernel("sharpi_latent_down_post")(down.data_ptr(), ld, q_rank, rank, rot, rot_dims if inv_freq is not None else 0,
+                                            _ptr(q_norm_weight), c_norm_weight.data_ptr(), float(eps), positions.data_ptr(),
+                                            row_req.data_ptr(), block_table.data_ptr(), block_table.shape[-1], page_size,
+                                            _ptr(inv_freq), cq.data_ptr(), kv_layer.data_ptr(), planes, D, int(write_kv),
+                                            dtype_code(kv_layer.dtype), T, _stream()), "sharpi_latent_down_post")
+    return cq
+
+
+def head_major(src: torch.Tensor, *, heads: int, stride: int, col0: int, n: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """Columns ``[col0, col0 + n)`` of every head of ``src [T, heads * stride]`` as ``[heads * T, n]`` (head by head,
+    the rows of a head in order) in ``out_dtype``: the operand of a product with one weight a head."""
+    _need(src, "src")
+    T = src.shape[0]
+    if src.shape[1] != heads * stride:
+        raise KernelError(f"src is {tuple(src.shape)}, expected [T, {heads} * {stride}]")
+    out = torch.empty((heads * T, n), dtype=out_dtype, device=src.device)
+    check(kernel("sharpi_head_major")(src.data_ptr(), dtype_code(src.dtype), T, heads, stride, col0, n, out.data_ptr(),
+                                      dtype_code(out_dtype), _stream()), "sharpi_head_major")
+    return out
+
+
+def head_minor(src: torch.Tensor, *, heads: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """``src`` float32 ``[heads * T, n]`` (head by head) as ``[T, heads * n]`` in ``out_dtype``."""
+    _need(src, "src", torch.float32)
+    n = src.shape[1]
+    T = src.shape[0] // heads
+    out = torch.empty((T, heads * n), dtype=out_dtype, device=src.device)
+    check(kernel("sharpi_head_minor")(src.data_ptr(), T, heads, n, 0, n, out.data_ptr(), dtype_code(out_dtype), _stream()),
+          "sharpi_head_minor")
+    return out
+
+
+def latent_q_join(qa: torch.Tensor, q: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor], *,
+                  heads: int, dim: int, rank: int, rot: int, rot_dims: int, D: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """The query rows of latent attention, ``[T, heads, D]``: ``[qa[h, t] | rotate(q[t, h, dim:]) | 0]`` with ``qa``
+    float32 ``[heads * T, rank]`` (head by head) and ``q`` float32 ``[T, heads * (dim + rot)]``."""
+    _need(qa, "qa", torch.float32)
+    _need(q, "q", torch.float32)
+    T = q.shape[0]
+    if q.shape[1] != heads * (dim + rot) or tuple(qa.shape) != (heads * T, rank):
+        raise KernelError(f"q {tuple(q.shape)} or qa {tuple(qa.shape)} disagree with the sizes")
+    out = torch.empty((T, heads, D), dtype=out_dtype, device=q.device)
+    check(kernel("sharpi_latent_q_join")(qa.data_ptr(), q.data_ptr(), positions.data_ptr(), _ptr(inv_freq), T, heads, dim,
+                                         rank, rot, rot_dims if inv_freq is not None else 0, D, out.data_ptr(),
+                                         dtype_code(out_dtype), _stream()), "sharpi_latent_q_join")
+    return out
+
+
+SSD_MAX_STATES = 256
+
+
+def ssd_scan(xbc: torch.Tensor, proj: torch.Tensor, *, col_x: int, col_b: int, col_c: int, col_dt: int,
+             dt_bias: torch.Tensor, a_log: torch.Tensor, dskip: torch.Tensor, row_offsets: torch.Tensor,
+             state_slots: torch.Tensor, state: torch.Tensor, heads: int, groups: int, states: int, vdim: int) -> torch.Tensor:
+    """The state-space-duality recurrence over the rows of every request, from and into ``state [slots, heads *
+    states * vdim]``: ``y`` float32 ``[T, heads * vdim]``.  ``xbc`` float32 holds x, B and C at the given columns,
+    ``proj`` float32 the raw step sizes at ``col_dt``; ``dt = softplus(raw + dt_bias)``, decay ``exp(-exp(A_log) dt)``."""
+    for name, t in (("xbc", xbc), ("proj", proj), ("dt_bias", dt_bias), ("a_log", a_log), ("dskip", dskip), ("state", state)):
+        _need(t, name, torch.float32)
+    T = xbc.shape[0]
+    if state.shape[-1] != heads * states * vdim or min(dt_bias.numel(), a_log.numel(), dskip.numel()) < heads:
+        raise KernelError("scan inputs disagree on heads, states or the value size")
+    y = torch.empty((T, heads * vdim), dtype=torch.float32, device=xbc.device)
+    check(kernel("sharpi_ssd_scan")(xbc.data_ptr(), xbc.shape[1], col_x, col_b, col_c, proj.data_ptr(), proj.shape[1], col_dt,
+                                    dt_bias.data_ptr(), a_log.data_ptr(), dskip.data_ptr(), row_offsets.data_ptr(),
+                                    state_slots.data_ptr(), state.data_ptr(), state.stride(0), y.data_ptr(), T,
+                                    state_slots.numel(), heads, groups, states, vdim, _stream()), "sharpi_ssd_scan")
+    return y
+
+
+def gated_group_norm(y: torch.Tensor, proj: torch.Tensor, col_z: int, weight: torch.Tensor, eps: float, parts: int,
+                     out_dtype: torch.dtype) -> torch.Tensor:
+    """``u = y * silu(z)`` with ``z`` the columns of ``proj`` from ``col_z``; ``u`` divided by its root mean square in
+    ``parts`` equal parts of the width, times ``weight``; ``[T, width]`` in ``out_dtype``."""
+    _need(y, "y", torch.float32)
+    _need(proj, "proj", torch.float32)
+    _need(weight, "weight", torch.float32)
+    T, width = y.shape
+    if col_z + width > proj.shape[1] or weight.numel() != width or width % parts:
+        raise KernelError("the gate's columns, the weight or the parts disagree with the width")
+    out = torch.empty((T, width), dtype=out_dtype, device=y.device)
+    z = proj[:, col_z:]
+    check(kernel("sharpi_gated_group_norm")(y.data_ptr(), z.data_ptr(), proj.shape[1], weight.data_ptr(), float(eps), T, width,
+                                            parts, out.data_ptr(), dtype_code(out_dtype), _stream()), "sharpi_gated_group_norm")
+    return out
+
+
+def sigmoid_gate(o: torch.Tensor, g: torch.Tensor) -> torch.Tensor:
+    """``o * sigmoid(g)`` element by element: ``o`` in the activation dtype, ``g`` float32 of the same shape."""
+    _need(o, "o")
+    _need(g, "g", torch.float32)
+    if o.shape != g.shape:
+        raise KernelError(f"shapes differ: {tuple(o.shape)}, {tuple(g.shape)}")
+    out = torch.empty_like(o)
+    check(kernel("sharpi_sigmoid_gate")(o.data_ptr(), g.data_ptr(), out.data_ptr(), dtype_code(o.dtype), o.numel(), _stream()),
+          "sharpi_sigmoid_gate")
+    return out

@@ -30,10 +30,10 @@ class DecoderModel:
     def __init__(self, *, embedding: torch.Tensor, blocks: Sequence[Block], final_norm: Norm, head: Linear,
                  act_dtype: torch.dtype, schedule: Optional[Sequence[ScheduleEntry]] = None,
                  eos_token_ids: Sequence[int] = (), config=None, stream_ops: Sequence[StreamOp] = (),
-                 embedder=None, logit_scale: float = 1.0):
+                 embedder=None, logit_scale: float = 1.0, embedding_scale: float = 1.0):
         """``embedder``: a part whose ``forward(ctx)`` gives the float32 residual stream(s) of the step's rows
         in place of the plain table lookup (its ``state_specs`` become per-request state of the model);
-        ``logit_scale`` multiplies the head's output."""
+        ``logit_scale`` multiplies the head's output, ``embedding_scale`` the looked-up embedding row."""
         self.embedding = embedding                  # [V, H]
         self.blocks: List[Block] = list(blocks)
         self.stream_ops: List[StreamOp] = list(stream_ops)
@@ -48,6 +48,7 @@ class DecoderModel:
         self.embedder = embedder
         self.state_specs = dict(getattr(embedder, "state_specs", None) or {})
         self.logit_scale = float(logit_scale)
+        self.embedding_scale = float(embedding_scale)
         self._validate_schedule()
 
     def set_schedule(self, schedule: Sequence[ScheduleEntry]) -> "DecoderModel":
@@ -79,6 +80,8 @@ class DecoderModel:
         """Run the step's rows through every scheduled block; float32 logits ``[R, V]`` at
         ``ctx.want_rows`` (None if no logits are wanted)."""
         x = self.embedder.forward(ctx) if self.embedder is not None else ops.embed_gather(ctx.token_ids, self.embedding)
+        if self.embedding_scale != 1.0:
+            ops.scale_(x, self.embedding_scale)
         # stream operations read the embedding output; the blocks add into x in place, so it is gathered twice
         x0 = ops.embed_gather(ctx.token_ids, self.embedding) if self.stream_ops else None
         pending = None

@@ -11,6 +11,12 @@ What the reference lacks is a parameter here: the mask (``full``, ``chunk`` of C
 ``1 + attn_scale * ln(1 + floor((pos + 1) / floor_scale))``, the score factor (``softmax_scale``), and a value
 size that differs from the key size (``value_dim``).
 
+Further parameters that other designs use: values that are the keys themselves (``values_are_keys``: no value
+projection, and a page holds keys only), a sliding window that keeps a sequence's first positions visible
+(``keep_first``), a learned number added to every score by the distance between query and key
+(``distance_bias``, a table by distance built with :func:`distance_bias_table`), and a sigmoid gate on the
+concatenated heads before the output projection (``gate``).
+
 Unequal key and value sizes: the kernels and the pages know one head size, so the part pads both to a common
 size D once, when it is built: zero rows in the fused projection (a padded q, k or v element is an exact zero),
 zero columns in the output projection.  Zeros change neither a score nor a rotation (the padded pairs get
@@ -78,6 +84,35 @@ class PagedAttentionPlanner(StepPlanner):
                     "decode_keys": keys if bucket is None else int(bucket)})
 
 
+def distance_bucket(n: int, rows: int, far: int) -> int:
+    """The row of a distance table with ``rows`` rows for the distance ``n >= 0``: distances below ``rows / 2`` have
+    a row each, the rows above are spread logarithmically up to the distance ``far``, beyond which the last row
+    stands: ``min(rows - 1, half + floor(ln(n / half) / ln(far / half) * (rows - half)))``, in float64."""
+    half = rows // 2
+    if n < half:
+        return n
+    if far <= half:
+        return rows - 1
+    return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+
+
+def distance_bias_table(rel: torch.Tensor, far: int) -> torch.Tensor:
+    """``rel [rows, heads]`` (a learned number per distance bucket and head) laid out by distance: float32
+    ``[n + 1, heads]`` whose row ``d`` is the bucket of distance ``d`` and whose last row holds for every larger
+    distance (the attention kernels read ``min(distance, n)``).  ``n`` is the first distance whose bucket is the
+    last row, so the table is never longer than ``far + 1`` rows."""
+    rows = rel.shape[0]
+    buckets = []
+    for n in range(max(int(far), rows) + 1):
+        buckets.append(distance_bucket(n, rows, int(far)))
+        if buckets[-1] == rows - 1:
+            break
+    if rel.device.type == "meta":
+        return torch.empty((len(buckets), rel.shape[1]), dtype=torch.float32, device="meta")
+    index = torch.tensor(buckets, dtype=torch.long, device=rel.device)
+    return rel.to(torch.float32)[index].contiguous()
+
+
 def _pad_projections(qkv: Linear, out: Linear, nq: int, nkv: int, dk: int, dv: int, D: int):
     """The fused q|k|v projection and the output projection with every head padded to ``D`` elements: zero rows
     (and zero bias entries) behind each head of q, k and v, zero columns behind each head in ``out``."""
@@ -107,7 +142,8 @@ class PagedAttention(Mixer):
                  temperature: Optional[Tuple[float, float]] = None,
                  softmax_scale: Optional[float] = None, act_dtype: torch.dtype = torch.bfloat16,
                  value_dim: Optional[int] = None, value_position: Optional[PositionEncoding] = None,
-                 k_norm: Optional[Norm] = None):
+                 k_norm: Optional[Norm] = None, values_are_keys: bool = False, keep_first: int = 0,
+                 distance_bias: Optional[torch.Tensor] = None, gate: Optional[Linear] = None):
         """``qk_norm``: any :class:`Norm` over the head size, applied to every head of q and k; after the
         position encoding (Llama 4's order) unless ``qk_norm_first``.  The weightless L2 norm after a rotation
         runs inside the kernel that rotates and writes the cache; every other combination applies the norm as
@@ -120,7 +156,14 @@ class PagedAttention(Mixer):
         ``k_norm``: the norm of k when it is not the one of q (``qk_norm``).  A rotation of only the leading
         elements of a head (``RotaryEncoding(rot_dims=...)``), rotated values, and a weighted norm before the
         rotation together with unequal key and value sizes run in the general form of the fused kernel
-        (``sharpi_qkv_post_rot``): norm first (``qk_norm_first``), then the rotation, then the cache write."""
+        (``sharpi_qkv_post_rot``): norm first (``qk_norm_first``), then the rotation, then the cache write.
+
+        ``values_are_keys``: ``qkv`` holds q and k only, a page holds keys only and attention sums the keys it
+        weighted.  ``keep_first`` (window mask): the first positions of a sequence stay visible.
+        ``distance_bias``: float32 ``[n + 1, heads]`` added to the scaled score by distance
+        (:func:`distance_bias_table`).  ``gate``: a projection of the mixer's input whose sigmoid multiplies the
+        concatenated heads.  A layer with kept positions or a distance bias, or with keys-only pages, runs the
+        general attention kernel."""
         if num_heads % num_kv_heads != 0:
             raise ValueError(f"heads ({num_heads}) must be a multiple of kv heads ({num_kv_heads})")
         key_dim = head_dim
@@ -128,9 +171,21 @@ class PagedAttention(Mixer):
         if key_dim <= 0 or value_dim <= 0 or key_dim % 2 != 0 or max(key_dim, value_dim) > 512:
             raise ValueError(f"head sizes {key_dim} (keys) and {value_dim} (values) are not supported: the key size "
                              f"must be even and both at most 512")
-        if qkv.out_features != (num_heads + num_kv_heads) * key_dim + num_kv_heads * value_dim:
+        if values_are_keys:
+            if value_dim != key_dim or value_position is not None:
+                raise ValueError("values that are the keys have the keys' size and no rotation of their own")
+            if position is not None and getattr(position, "rot_dims", None) is not None:
+                raise ValueError("values that are the keys are not built with a rotation of a head's leading elements")
+        if keep_first and mask != "window":
+            raise ValueError("kept first positions belong to the window mask")
+        if distance_bias is not None and (distance_bias.dim() != 2 or distance_bias.shape[1] != num_heads):
+            raise ValueError(f"the distance bias is {tuple(distance_bias.shape)}, expected [distances, {num_heads}]")
+        if gate is not None and gate.out_features != num_heads * value_dim:
+            raise ValueError(f"the gate has {gate.out_features} rows, expected heads * value_dim = {num_heads * value_dim}")
+        v_rows = 0 if values_are_keys else num_kv_heads * value_dim
+        if qkv.out_features != (num_heads + num_kv_heads) * key_dim + v_rows:
             raise ValueError(f"fused qkv weight has {qkv.out_features} rows, expected (heads + kv_heads) * head_dim + "
-                             f"kv_heads * value_dim = {(num_heads + num_kv_heads) * key_dim + num_kv_heads * value_dim}")
+                             f"kv_heads * value_dim = {(num_heads + num_kv_heads) * key_dim + v_rows}")
         if out.in_features != num_heads * value_dim:
             raise ValueError(f"output projection reads {out.in_features} columns, expected {num_heads * value_dim}")
         self.key_dim, self.value_dim = key_dim, value_dim
@@ -178,7 +233,11 @@ class PagedAttention(Mixer):
                 position = type(position)(wide, pairing)
         self.qkv, self.out = qkv, out
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
-        self.cache_spec = CacheSpec(mask, span if mask != "full" else 0, num_kv_heads, head_dim)
+        self.cache_spec = CacheSpec(mask, span if mask != "full" else 0, num_kv_heads, head_dim,
+                                    planes=1 if values_are_keys else 2, keep_first=int(keep_first))
+        self.values_are_keys, self.keep_first, self.distance_bias, self.gate = values_are_keys, int(keep_first), distance_bias, gate
+        # what the tensor-core attention kernels do not take runs the general kernel
+        self._general_attention = values_are_keys or self.keep_first > 0 or distance_bias is not None
         self.position = position
         self.qk_norm = qk_norm
         self.qk_norm_first = bool(qk_norm_first)
@@ -221,7 +280,7 @@ class PagedAttention(Mixer):
         table = ctx.block_tables[slot.group]
         qkv = self.qkv(h)                                                       # [T, (nq + 2 nkv) d] float32
         if self._general:
-            return self._forward_general(ctx, slot, plan, table, qkv)
+            return self._forward_general(ctx, slot, plan, table, qkv, h)
 
         rot = self.position.rotary() if self.position is not None else None
         if self.position is not None and rot is None and type(self.position).apply is not PositionEncoding.apply:
@@ -243,8 +302,11 @@ class PagedAttention(Mixer):
                      page_size=slot.page_size, pairing=pairing,
                      l2_eps=self.qk_norm.eps if self._norm_fused else -1.0,
                      temp_attn_scale=attn_scale, temp_floor_scale=floor_scale, write_kv=slot.writes_cache,
-                     l2_count=self.key_dim)
-        return self.out(self._attend(ctx, slot, plan, table, q))
+                     l2_count=self.key_dim, kv_planes=self.cache_spec.planes)
+        o = self._attend(ctx, slot, plan, table, q)
+        if self.gate is not None:
+            o = ops.sigmoid_gate(o.view(T, -1), self.gate(h))
+        return self.out(o)
 
     def _norm_weight(self, norm: Optional[Norm], device) -> Optional[torch.Tensor]:
         if norm is None:
@@ -256,7 +318,8 @@ class PagedAttention(Mixer):
             w = self._ones
         return w
 
-    def _forward_general(self, ctx: StepContext, slot: LayerSlot, plan, table, qkv: torch.Tensor) -> torch.Tensor:
+    def _forward_general(self, ctx: StepContext, slot: LayerSlot, plan, table, qkv: torch.Tensor,
+                         h: torch.Tensor) -> torch.Tensor:
         T, nq, nkv, d = ctx.num_tokens, self.num_heads, self.num_kv_heads, self.head_dim
         rot = self.position.rotary() if self.position is not None else None
         vrot = self.value_position.rotary() if self.value_position is not None else None
@@ -274,13 +337,15 @@ class PagedAttention(Mixer):
         if vrot is not None:                # every head's sum of rotated values, turned back by the row's position
             o = ops.rotate_heads(o, ctx.positions, vrot[0], heads=nq, D=d, rot_dims=self._v_rot_dims, pairing=pairing,
                                  sign=-1.0, out_dtype=self.act_dtype)
+        if self.gate is not None:
+            o = ops.sigmoid_gate(o.view(T, -1), self.gate(h))
         return self.out(o)
 
     def _attend(self, ctx: StepContext, slot: LayerSlot, plan, table, q: torch.Tensor) -> torch.Tensor:
         T, nq, nkv, d = ctx.num_tokens, self.num_heads, self.num_kv_heads, self.head_dim
         h = q
         mask_kind, mask_span = _MASK_CODE[self.cache_spec.kind], max(self.cache_spec.span, 1)
-        if self.act_dtype == torch.bfloat16 and d in ops.FAST_ATTENTION_HEAD_SIZES:
+        if self.act_dtype == torch.bfloat16 and d in ops.FAST_ATTENTION_HEAD_SIZES and not self._general_attention:
             # tensor-core kernels: tiles of prompt rows, and single rows split over their keys
             o = torch.empty((T, nq * d), dtype=torch.bfloat16, device=h.device)
             if plan.num_tiles:
@@ -295,5 +360,6 @@ class PagedAttention(Mixer):
         else:
             o = ops.paged_attention_generic(q, slot.kv, table, ctx.row_request, ctx.positions, nq=nq, nkv=nkv, d=d,
                                             page_size=slot.page_size, mask_kind=mask_kind, mask_span=mask_span,
-                                            scale=self.softmax_scale)
+                                            scale=self.softmax_scale, keep_first=self.keep_first,
+                                            dist_bias=self.distance_bias)
         return o

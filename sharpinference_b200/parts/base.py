@@ -43,18 +43,28 @@ class CacheSpec:
     ``kind`` is ``"full"`` (every earlier position), ``"chunk"`` (positions of the same chunk of
     ``span`` positions) or ``"window"`` (the last ``span`` positions, the query's own included).
     Layers with equal specs share one group of pages and one block table per request.
+
+    ``planes``: 2 when a page holds keys and values, 1 when it holds keys only and a value is its key row (the
+    values are the keys, or both are readings of one cached latent).  ``keep_first`` (window kind): the first
+    positions of a sequence stay visible whatever the window, so the pages that hold them are never given back.
     """
 
     kind: str
     span: int
     num_kv_heads: int
     head_dim: int
+    planes: int = 2
+    keep_first: int = 0
 
     def __post_init__(self):
         if self.kind not in ("full", "chunk", "window"):
             raise ValueError(f"cache kind '{self.kind}' is not one of full, chunk, window")
         if self.kind != "full" and self.span <= 0:
             raise ValueError(f"cache kind '{self.kind}' needs a positive span, found {self.span}")
+        if self.planes not in (1, 2):
+            raise ValueError(f"a page holds 1 or 2 planes, found {self.planes}")
+        if self.keep_first < 0 or (self.keep_first and self.kind != "window"):
+            raise ValueError(f"keep_first ({self.keep_first}) must not be negative and belongs to the window kind")
 
     def lowest_visible(self, pos: int) -> int:
         """The lowest position a query at ``pos`` may read."""
@@ -80,7 +90,7 @@ class LayerSlot:
     index: int                              # place in the schedule
     layer: int                              # which block runs there
     group: Optional[int] = None             # id of the page group (key of StepContext.block_tables)
-    kv: Optional[torch.Tensor] = None       # [pages, 2, kv_heads, page_size, head_dim]
+    kv: Optional[torch.Tensor] = None       # [pages, planes, kv_heads, page_size, head_dim]
     writes_cache: bool = True               # False: reads the cache that another entry writes
     state: Optional[torch.Tensor] = None    # [state_slots, *StateSpec.shape]
     page_size: int = 0

@@ -256,3 +256,80 @@ class MoESigmoidTopK(FeedForward):
             ops.gemm_nt(act, self.experts_down.weight, out=y, group_offsets=offsets, out_rows=sorted_pairs, rows=T * k,
                         row_scale=weight.view(-1), scale_rows=sorted_pairs)
         return ops.moe_combine(y, k, add=add_to, out=add_to)
+
+
+@register_part("feed_forward", "moe_sigmoid_topk_gated")
+class MoESigmoidTopKGated(FeedForward):
+    """A mixture of ``E`` gated experts (``W_down (silu(W_gate u) * (W_up u))``, no biases) of which every row uses
+    ``top_k``, with an optional shared expert of the same form that every row uses.
+
+    Router: ``s = sigmoid(Wr h)`` in float32 on the unrounded activations; the ``top_k`` experts with the largest
+    ``s`` are chosen (the lowest index wins among equals); the chosen scores are the weights as they are (divided by
+    their sum first when ``renormalize``).  A weight multiplies its expert's *input*: the routed output is
+    ``sum_e expert_e(s_e h)``.  Because gate and up are linear in their input, the weight is applied to both products
+    in the first grouped product's epilogue, before the nonlinearity.  The (row, choice) pairs are sorted by expert on
+    the device, each expert multiplies its rows in one grouped product (tcgen05 for bfloat16 weights whose inner
+    sizes are multiples of 8, CUDA cores otherwise), and the pairs of a row are added in the order of the choices
+    together with the shared expert's output, so a row's result does not depend on the rest of the step.
+
+    With one expert a row this is the arithmetic of :class:`MoESigmoidTop1`, which fuses more and is what a builder
+    should pick then; this part takes any ``top_k``.
+    """
+
+    wants_fp32_input = True
+    graph_safe = True
+    adds_to = True
+
+    def __init__(self, *, router: torch.Tensor, experts_gate_up: GroupedLinear, experts_down: GroupedLinear, top_k: int,
+                 shared: Optional[DenseSwiGLU] = None, renormalize: bool = False,
+                 act_dtype: torch.dtype = torch.bfloat16):
+        E = experts_gate_up.num_groups
+        if router.shape != (E, experts_gate_up.in_features):
+            raise ValueError(f"router weight is {tuple(router.shape)}, expected [{E}, {experts_gate_up.in_features}]")
+        if experts_down.num_groups != E or experts_gate_up.out_features != 2 * experts_down.in_features:
+            raise ValueError("expert gate|up and down weights disagree on the number or width of the experts")
+        if not (1 <= top_k <= min(E, 32)):
+            raise ValueError(f"experts per row must be 1 .. min(experts, 32), found {top_k} of {E}")
+        self.router = router
+        self.experts_gate_up, self.experts_down, self.shared = experts_gate_up, experts_down, shared
+        self.num_experts, self.top_k, self.renormalize, self.act_dtype = E, int(top_k), bool(renormalize), act_dtype
+        self._tensor_core = (experts_gate_up.weight.dtype == torch.bfloat16
+                             and experts_down.weight.dtype == torch.bfloat16 and act_dtype == torch.bfloat16
+                             and experts_gate_up.in_features % 8 == 0 and experts_down.in_features % 8 == 0)
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, h32: Optional[torch.Tensor] = None,
+                add_to: Optional[torch.Tensor] = None) -> torch.Tensor:
+        T, k = h.shape[0], self.top_k
+        if h32 is None:
+            h32 = h.to(torch.float32)
+        # the shared expert meets the routed ones only in the last sum: it runs on a second stream meanwhile
+        main = torch.cuda.current_stream(h.device)
+        base = add_to
+        side = None
+        if self.shared is not None:
+            side = _side_stream(h.device)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                if base is not None:
+                    self.shared.forward(ctx, h, out=base, accumulate=True)
+                else:
+                    base = self.shared.forward(ctx, h)
+        expert, weight, _ = ops.router_topk(h32, self.router, k, renormalize=self.renormalize)
+        if "router_choices" in ctx.extras:          # tracing: which experts every row went to
+            ctx.extras["router_choices"].append(expert)
+        offsets, sorted_pairs = ops.moe_sort(expert.view(-1), self.num_experts)     # pair = row * k + choice
+        pair_rows = ops.moe_pair_tokens(sorted_pairs, k) if k > 1 else sorted_pairs
+        y = torch.empty((T * k, self.experts_down.out_features), dtype=torch.float32, device=h.device)
+        if self._tensor_core and h.dtype == torch.bfloat16:
+            h_sorted = ops.gather_rows_bf16(h, pair_rows)
+            act = ops.tc_grouped_gemm(h_sorted, self.experts_gate_up.weight, offsets, mode=ops.TC_MODE_SWIGLU,
+                                      row_scale=weight.view(-1), scale_rows=sorted_pairs)
+            ops.tc_grouped_gemm(act, self.experts_down.weight, offsets, mode=ops.TC_MODE_STORE, out=y,
+                                out_rows=sorted_pairs)
+        else:
+            gu = self.experts_gate_up(h, offsets, rows=T * k, a_rows=pair_rows)        # sorted order
+            act = ops.swiglu(gu, self.act_dtype, row_scale=weight.view(-1), scale_rows=sorted_pairs)
+            self.experts_down(act, offsets, rows=T * k, out_rows=sorted_pairs, out=y)
+        if side is not None:
+            main.wait_stream(side)
+        return ops.moe_combine(y, k, add=base, out=base)

@@ -1,0 +1,106 @@
+"""Latent attention: queries, keys and values all pass through low-rank latents, and only the key/value latent and
+one small rotated key part are cached.
+
+For the mixer's input ``h`` (``H`` heads; per head ``dim`` unrotated and ``rot`` rotated query/key elements, values of
+``vdim``; latents of ``q_rank`` and ``rank`` elements):
+
+    c_q = rms(W_dq h) * w_q                      q = W_uq c_q          per head [q_plain (dim) | q_rot (rot)]
+    [c_raw | k_rot] = W_dkv h                    c = rms(c_raw) * w_c  k_rot is shared by all heads
+    score_h(i, j) = (q_plain_h(i) . (W_uk_h c(j)) + R_i q_rot_h(i) . R_j k_rot(j)) * scale,   j <= i
+    out = W_o concat_h( softmax_j(score_h) . (W_uv_h c(j)) )
+
+with ``R_p`` the rotation of pairs ``(2i, 2i + 1)`` of the first ``rot_dims`` rotated elements by ``p * f_i``.
+
+The unrotated score is ``(W_uk_h^T q_plain_h(i)) . c(j)``, and a head's value sum is ``W_uv_h (sum_j p_j c(j))``, so the
+cache holds one row ``[c | R k_rot]`` per token for all heads (a cache group with one key/value head and keys-only
+pages), the query of a head becomes ``[W_uk_h^T q_plain_h | R q_rot_h]``, the paged attention kernels run as for one
+shared key/value head whose value is its key row, and ``W_uv_h`` expands the leading ``rank`` elements of a head's
+output.  The two per-head products are grouped products with the heads as groups.  Norm sums, angles, scores and
+softmax are float32; the latents, queries and the cache are rounded to the activation dtype where they enter a
+product.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..kernels import ops
+from .base import CacheSpec, LayerSlot, Mixer, PositionEncoding, StepContext, register_part
+from .attention import PagedAttentionPlanner
+from .linear import GroupedLinear, Linear
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Mixer):
+    graph_safe = True
+
+    def __init__(self, *, down: Linear, q_norm_weight: torch.Tensor, c_norm_weight: torch.Tensor, up_q: Linear,
+                 up_k: GroupedLinear, up_v: GroupedLinear, out: Linear, num_heads: int, dim: int, rot_dim: int,
+                 value_dim: int, q_rank: int, kv_rank: int, eps: float, softmax_scale: float,
+                 position: Optional[PositionEncoding] = None, act_dtype: torch.dtype = torch.bfloat16):
+        """``down``: the fused down projections, rows ``[W_dq (q_rank) | W_dkv (kv_rank + rot_dim)]``.
+        ``up_k``: per head ``W_uk_h^T`` as a group ``[kv_rank, dim]`` (it maps a head's unrotated query into the
+        latent); ``up_v``: per head ``W_uv_h [value_dim, kv_rank]``.  ``position``: a rotary encoding of neighbouring
+        pairs over the first ``rot_dims`` of the ``rot_dim`` rotated elements (None: no rotation)."""
+        H = num_heads
+        if down.out_features != q_rank + kv_rank + rot_dim:
+            raise ValueError(f"the fused down projection has {down.out_features} rows, expected q_rank + kv_rank + "
+                             f"rot_dim = {q_rank + kv_rank + rot_dim}")
+        if up_q.in_features != q_rank or up_q.out_features != H * (dim + rot_dim):
+            raise ValueError(f"the query up projection is [{up_q.out_features}, {up_q.in_features}], expected "
+                             f"[{H * (dim + rot_dim)}, {q_rank}]")
+        if (up_k.num_groups, up_k.out_features, up_k.in_features) != (H, kv_rank, dim):
+            raise ValueError(f"up_k must hold [{H}, {kv_rank}, {dim}] (a head's key projection, transposed)")
+        if (up_v.num_groups, up_v.out_features, up_v.in_features) != (H, value_dim, kv_rank):
+            raise ValueError(f"up_v must hold [{H}, {value_dim}, {kv_rank}]")
+        if out.in_features != H * value_dim:
+            raise ValueError(f"output projection reads {out.in_features} columns, expected {H * value_dim}")
+        if q_norm_weight.numel() != q_rank or c_norm_weight.numel() != kv_rank:
+            raise ValueError("the latents' norm weights disagree with q_rank or kv_rank")
+        self.inv_freq, self.rot_dims = None, 0
+        if position is not None and rot_dim:
+            rot = position.rotary()
+            if rot is None or rot[1] != "interleaved":
+                raise ValueError("latent attention rotates neighbouring pairs (a rotary encoding, interleaved)")
+            self.rot_dims = position.rot_dims if getattr(position, "rot_dims", None) is not None else rot_dim
+            if self.rot_dims > rot_dim or self.rot_dims % 2 or rot[0].numel() != self.rot_dims // 2:
+                raise ValueError(f"{self.rot_dims} rotated elements do not fit the rotated part of {rot_dim}")
+            self.inv_freq = rot[0] if self.rot_dims else None
+        self.down, self.up_q, self.up_k, self.up_v, self.out = down, up_q, up_k, up_v, out
+        self.q_norm_weight, self.c_norm_weight = q_norm_weight, c_norm_weight
+        self.num_heads, self.dim, self.rot_dim, self.value_dim = H, dim, rot_dim, value_dim
+        self.q_rank, self.kv_rank, self.eps = q_rank, kv_rank, float(eps)
+        self.softmax_scale, self.act_dtype = float(softmax_scale), act_dtype
+        # one cached row a token: [c | k_rot], padded to what the attention kernels take as a head size
+        D = kv_rank + rot_dim
+        D = (D + 15) // 16 * 16 if D <= 128 else D + (D & 1)
+        if D > 512:
+            raise ValueError(f"kv_rank + rot_dim = {kv_rank + rot_dim} exceeds the largest head size of the attention "
+                             f"kernels (512)")
+        self.head_dim = D
+        self.cache_spec = CacheSpec("full", 0, 1, D, planes=1)
+
+    def step_planner(self, page_size: int):
+        return PagedAttentionPlanner(64)
+
+    def forward(self, ctx: StepContext, slot: LayerSlot, h: torch.Tensor) -> torch.Tensor:
+        T, H, D, act = ctx.num_tokens, self.num_heads, self.head_dim, self.act_dtype
+        table = ctx.block_tables[slot.group]
+        down = self.down(h)                                                   # [T, q_rank + kv_rank + rot] float32
+        cq = ops.latent_down_post(down, q_rank=self.q_rank, rank=self.kv_rank, rot=self.rot_dim, rot_dims=self.rot_dims,
+                                  q_norm_weight=self.q_norm_weight, c_norm_weight=self.c_norm_weight, eps=self.eps,
+                                  positions=ctx.positions, row_req=ctx.row_request, block_table=table,
+                                  inv_freq=self.inv_freq, kv_layer=slot.kv, page_size=slot.page_size,
+                                  write_kv=slot.writes_cache)
+        q = self.up_q(cq)                                                     # [T, H (dim + rot)] float32
+        q_plain = ops.head_major(q, heads=H, stride=self.dim + self.rot_dim, col0=0, n=self.dim, out_dtype=act)
+        qa = self.up_k.per_group(q_plain, T)                                  # [H T, kv_rank] float32
+        qj = ops.latent_q_join(qa, q, ctx.positions, self.inv_freq, heads=H, dim=self.dim, rank=self.kv_rank,
+                               rot=self.rot_dim, rot_dims=self.rot_dims, D=D, out_dtype=act)
+        o = ops.paged_attention_generic(qj, slot.kv, table, ctx.row_request, ctx.positions, nq=H, nkv=1, d=D,
+                                        page_size=slot.page_size, mask_kind=ops.MASK_FULL, mask_span=1,
+                                        scale=self.softmax_scale)
+        o_lat = ops.head_major(o, heads=H, stride=D, col0=0, n=self.kv_rank, out_dtype=act)
+        v = self.up_v.per_group(o_lat, T)                                     # [H T, value_dim] float32
+        return self.out(ops.head_minor(v, heads=H, out_dtype=act))

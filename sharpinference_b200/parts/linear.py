@@ -115,3 +115,14 @@ class GroupedLinear:
             a = a.to(torch.float32)
         return ops.gemm_nt(a, self.weight, out=out, group_offsets=group_offsets, a_rows=a_rows, out_rows=out_rows,
                            rows=rows, accumulate=accumulate)
+
+    def per_group(self, a: torch.Tensor, rows_per_group: int) -> torch.Tensor:
+        """The product for ``a [groups * rows_per_group, in]`` that holds every group's rows one group after the
+        other, the same number each (one weight a head: heads are the groups): float32 ``[groups * rows_per_group,
+        out]``.  bfloat16 operands with an inner size that is a multiple of 8 run the tcgen05 grouped product,
+        everything else the CUDA-core one."""
+        offsets = torch.arange(0, (self.num_groups + 1) * rows_per_group, max(rows_per_group, 1), dtype=torch.int32,
+                               device=a.device)
+        if (self.weight.dtype == torch.bfloat16 and a.dtype == torch.bfloat16 and self.in_features % 8 == 0):
+            return ops.tc_grouped_gemm(a, self.weight, offsets, mode=ops.TC_MODE_STORE)
+        return self(a, offsets, rows=a.shape[0])

@@ -1,4 +1,5 @@
-"""The selective state-space mixer (Mamba) and the mixer that runs two mixers side by side.
+"""The selective state-space mixer (Mamba), its state-space-duality form with a scalar decay per head (Mamba-2), and
+the mixer that runs two mixers side by side.
 
 ``SelectiveScanMixer``: ``W_in h = [x | z]`` (``inner`` channels each).  ``x`` passes a causal convolution per channel
 (``taps`` inputs, the last weight column is the current token's, zeros before a sequence's start) with a bias, then
@@ -11,6 +12,16 @@ and the result is ``W_o (y * silu(z))``.  The convolution, step sizes, exponenti
 the projections round their inputs to the activation dtype.  Per-request state: ``S`` (``state_specs["S"]``) and
 the convolution's last ``taps - 1`` inputs (``state_specs["conv"]``), both zero at a sequence's start
 (``csrc/mamba.cu``).
+
+``StateSpaceDualityMixer``: ``W_in h = [x (heads * vdim) | B (groups * states) | C (groups * states) | z (heads * vdim)
+| dt (heads)]`` (the builder orders the projection's rows so).  ``x``, ``B`` and ``C`` together pass the causal
+convolution with its bias and silu.  ``dt = softplus(dt + dt_bias)`` per head; per head ``h`` of group ``g``:
+
+    S_h <- exp(-exp(A_log_h) dt_h) S_h + dt_h B_g x_h^T     (S_h is states x vdim) ;   y_h = S_h^T C_g + D_h x_h
+
+then ``y * silu(z)`` is RMS-normed in ``norm_groups`` equal parts of its width, each by its own root mean square,
+times a weight, and ``W_o`` follows.  Convolution, step sizes, decays, state, sums and the norm are float32.
+Per-request state: ``S`` and the convolution's last ``taps - 1`` inputs (``csrc/mamba2.cu``, ``csrc/mamba.cu``).
 
 ``BranchPair``: two mixers that read the same input; the result is ``scale * (rms(left) * w_left + rms(right) *
 w_right)``, each branch's output normed over the model width with a plain weight first.  The pair owns the cache
@@ -63,6 +74,62 @@ class SelectiveScanMixer(Mixer):
                                self.d_skip, xz, self.inner, row_offsets=ctx.row_offsets, state_slots=ctx.state_slots,
                                state=slot.states["S"], out_dtype=self.act_dtype)
         return self.out(y)
+
+
+@register_part("mixer", "state_space_duality")
+class StateSpaceDualityMixer(Mixer):
+    graph_safe = True
+    cache_spec = None
+
+    def __init__(self, *, in_proj: Linear, conv_weight: torch.Tensor, conv_bias: Optional[torch.Tensor],
+                 dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor, norm_weight: torch.Tensor,
+                 out: Linear, heads: int, value_dim: int, states: int, groups: int, taps: int, norm_groups: int,
+                 eps: float, act_dtype: torch.dtype = torch.bfloat16):
+        """``in_proj``: rows ``[x | B | C | z | dt]`` (see :func:`ssd_projection_order` for the order a file that
+        stores ``[z | x | B | C | dt]`` is brought into)."""
+        inner, bc = heads * value_dim, groups * states
+        if heads % groups:
+            raise ValueError(f"heads ({heads}) must be a multiple of groups ({groups})")
+        if in_proj.out_features != 2 * inner + 2 * bc + heads or out.in_features != inner:
+            raise ValueError(f"the projections disagree with the inner size {inner}, {groups} groups of {states} states "
+                             f"and {heads} heads")
+        if conv_weight.numel() != (inner + 2 * bc) * taps or taps < 1:
+            raise ValueError("the convolution weight disagrees with the channels or the taps")
+        if states > ops.SSD_MAX_STATES or inner % norm_groups or norm_weight.numel() != inner:
+            raise ValueError(f"{states} states (at most {ops.SSD_MAX_STATES}) or {norm_groups} norm groups over {inner} "
+                             f"are not supported")
+        if min(dt_bias.numel(), a_log.numel(), d_skip.numel()) != heads:
+            raise ValueError("dt_bias, A_log and D hold one number a head")
+        self.in_proj, self.out = in_proj, out
+        self.conv_weight, self.conv_bias = conv_weight, conv_bias
+        self.dt_bias, self.a_log, self.d_skip, self.norm_weight = dt_bias, a_log, d_skip, norm_weight
+        self.heads, self.value_dim, self.states, self.groups = heads, value_dim, states, groups
+        self.taps, self.norm_groups, self.eps, self.act_dtype = taps, norm_groups, float(eps), act_dtype
+        self.inner, self.channels = inner, inner + 2 * bc
+        self.state_specs = {"S": StateSpec((heads * states * value_dim,), torch.float32),
+                            "conv": StateSpec((max(taps - 1, 1) * self.channels,), torch.float32)}
+
+    def forward(self, ctx: StepContext, slot: LayerSlot, h: torch.Tensor) -> torch.Tensor:
+        proj = self.in_proj(h)                                                   # [T, channels + inner + heads] float32
+        xbc, _ = ops.causal_conv(proj, self.channels, self.conv_weight, self.conv_bias, slot.states["conv"],
+                                 row_request=ctx.row_request, row_offsets=ctx.row_offsets,
+                                 state_slots=ctx.state_slots, act_dtype=torch.float32)
+        y = ops.ssd_scan(xbc, proj, col_x=0, col_b=self.inner, col_c=self.inner + self.groups * self.states,
+                         col_dt=self.channels + self.inner, dt_bias=self.dt_bias, a_log=self.a_log, dskip=self.d_skip,
+                         row_offsets=ctx.row_offsets, state_slots=ctx.state_slots, state=slot.states["S"],
+                         heads=self.heads, groups=self.groups, states=self.states, vdim=self.value_dim)
+        u = ops.gated_group_norm(y, proj, self.channels, self.norm_weight, self.eps, self.norm_groups, self.act_dtype)
+        return self.out(u)
+
+
+def ssd_projection_order(heads: int, value_dim: int, states: int, groups: int) -> torch.Tensor:
+    """Row indices that bring an input projection stored as ``[z | x | B | C | dt]`` into the order
+    ``[x | B | C | z | dt]`` that :class:`StateSpaceDualityMixer` reads (the convolved channels first)."""
+    inner, bc = heads * value_dim, groups * states
+    z = torch.arange(0, inner)
+    xbc = torch.arange(inner, 2 * inner + 2 * bc)
+    dt = torch.arange(2 * inner + 2 * bc, 2 * inner + 2 * bc + heads)
+    return torch.cat([xbc, z, dt])
 
 
 @register_part("mixer", "branch_pair")

@@ -1,4 +1,5 @@
-"""Norm parts: RMSNorm with a weight, and the weightless L2 norm used on q and k per head.
+"""Norm parts: RMSNorm with a weight, the weightless L2 norm used on q and k per head, and the element-wise
+squashing norm (``DynamicTanh``).
 
 RMSNorm: ``x * rsqrt(mean(x^2) + eps) * w`` (src/SharpInference.Cpu/SimdKernels.cs:4209-4246);
 the weightless form drops ``w`` (src/SharpInference.Cpu/SimdKernels.cs:4252-4283).  The sum of
@@ -37,3 +38,16 @@ class L2Norm(Norm):
 
     def apply(self, x, delta, *, rows=None, out_dtype=torch.bfloat16, want_fp32=False):
         return ops.add_rmsnorm(x, delta, None, self.eps, out_dtype, rows=rows, want_fp32=want_fp32)
+
+
+@register_part("norm", "dynamic_tanh")
+class DynamicTanh(Norm):
+    """``tanh(alpha x) w + b`` element by element, with one learned scalar ``alpha``: a norm that forms no mean and no
+    variance, so a row's element depends on that element alone.  Float32; the residual add is fused as in the others."""
+
+    def __init__(self, weight: torch.Tensor, bias: torch.Tensor, alpha: torch.Tensor):
+        self.weight, self.bias = weight, bias
+        self.alpha = alpha.reshape(1).to(torch.float32).contiguous()      # read on the device: nothing to bake into a graph
+
+    def apply(self, x, delta, *, rows=None, out_dtype=torch.bfloat16, want_fp32=False):
+        return ops.add_dyt(x, delta, self.weight, self.bias, self.alpha, out_dtype, rows=rows, want_fp32=want_fp32)
