@@ -84,10 +84,11 @@ def latent_attention(h, m, wt, p, eps):
     pos = torch.arange(T)
     cq = rms(h @ wt[p + "dq"].T, eps) * wt[p + "dq.norm"]
     q = (cq @ wt[p + "uq"].T).reshape(T, H, d + dr)
-    q_plain, q_rot = q[..., :d], rotate_pairs(q[..., d:], pos, m["rot"]["base"], m["rot"]["dims"])
+    rot = m.get("rot") or {"base": 10000.0, "dims": 0}
+    q_plain, q_rot = q[..., :d], rotate_pairs(q[..., d:], pos, rot["base"], rot["dims"])
     down = h @ wt[p + "dkv"].T
     c = rms(down[:, :r], eps) * wt[p + "dkv.norm"]
-    k_rot = rotate_pairs(down[:, None, r:], pos, m["rot"]["base"], m["rot"]["dims"])[:, 0]      # [T, dr]
+    k_rot = rotate_pairs(down[:, None, r:], pos, rot["base"], rot["dims"])[:, 0]      # [T, dr]
     k_plain = (c @ wt[p + "uk"].T).reshape(T, H, d)
     v = (c @ wt[p + "uv"].T).reshape(T, H, dv)
     out = torch.empty(T, H, dv, dtype=F64)
@@ -98,16 +99,19 @@ def latent_attention(h, m, wt, p, eps):
     return out.reshape(T, H * dv) @ wt[p + "o"].T
 
 
-def window_attention(h, m, wt, p):
+def window_attention(h, m, wt, p, window_delta=0, keep_delta=0):
     """Grouped-query attention whose values are its keys, with a learned bias by distance, a sliding window that
-    keeps the first tokens, and a sigmoid gate on the concatenated heads."""
+    keeps the first tokens, and a sigmoid gate on the concatenated heads.  The deltas make a deliberately wrong
+    window or kept count (for showing that a test would notice)."""
     T = h.shape[0]
-    H, G, d = m["heads"], m["kv_heads"], m["dim"]
+    H, G, d = m["heads"], m.get("kv_heads", m["heads"]), m["dim"]
     q = (h @ wt[p + "q"].T + wt[p + "q.b"]).reshape(T, H, d)
     k = (h @ wt[p + "k"].T + wt[p + "k.b"]).reshape(T, G, d)
     rel = wt[p + "rel"]
     rows = rel.shape[0]
-    vis = window_with_first(T, m["mask"]["size"], m["mask"]["keep_first"])
+    mask = m.get("mask")
+    vis = (window_with_first(T, mask["size"] + window_delta, max(mask.get("keep_first", 0) + keep_delta, 0))
+           if mask else causal(T))
     idx = torch.tensor([[distance_bucket(max(i - j, 0), rows, m["bias_max"]) for j in range(T)] for i in range(T)])
     out = torch.empty(T, H, d, dtype=F64)
     for hd in range(H):
@@ -132,7 +136,7 @@ def causal_conv_silu(x, w, b):
 def mamba2(h, m, wt, p, eps):
     """State-space duality layer walked token by token: a scalar decay per head, keys and queries (B, C) per group."""
     T = h.shape[0]
-    nh, dv, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
+    nh, dv, N, G = m["heads"], m["vdim"], m["state"], m.get("groups", 1)
     inner = nh * dv
     proj = h @ wt[p + "in"].T
     z, xbc, dt = proj[:, :inner], proj[:, inner:2 * inner + 2 * G * N], proj[:, 2 * inner + 2 * G * N:]
@@ -150,7 +154,7 @@ def mamba2(h, m, wt, p, eps):
             S[hd] = decay[t, hd] * S[hd] + dt[t, hd] * torch.outer(B[t, g], x[t, hd])
             y[t, hd] = S[hd].T @ C[t, g] + wt[p + "D"][hd] * x[t, hd]
     y = y.reshape(T, inner) * silu(z)
-    parts = m["norm_groups"]
+    parts = m.get("norm_groups", 1)
     y = rms(y.reshape(T, parts, inner // parts), eps).reshape(T, inner) * wt[p + "norm"]
     return y @ wt[p + "o"].T
 
@@ -175,12 +179,13 @@ def mixture(h, mlp, wt, p, choices=None):
     return out, scores, chosen
 
 
-def forward(config: dict, weights: dict, tokens, want_layers: bool = False, choices=None):
-    """Logits [T, vocab] for one sequence; with ``want_layers`` also the residual stream after every layer.
-    ``choices``: per routed layer (in order) a [T, top] tensor of expert ids to follow."""
+def forward(config: dict, weights: dict, tokens, want_layers: bool = False, choices=None, window_delta=0, keep_delta=0):
+    """Logits [T, vocab] for one sequence; with ``want_layers`` also the residual stream after every layer and the
+    router scores and choices of every routed layer.  ``choices``: per routed layer (in order) a [T, top] tensor of
+    expert ids to follow."""
     wt = {k: v.to(F64) for k, v in weights.items()}
     eps = config["norm"]["eps"]
-    x = wt["embed"][torch.tensor(tokens)] * config["embedding"]["scale"]
+    x = wt["embed"][torch.tensor(tokens)] * config.get("embedding", {}).get("scale", 1.0)
     after, routed, seen = [], 0, []
     for i, layer in enumerate(config["layers"]):
         p = f"l{i}."
@@ -188,7 +193,7 @@ def forward(config: dict, weights: dict, tokens, want_layers: bool = False, choi
         if layer["type"] == "latent_attention":
             x = x + latent_attention(h, layer["mixer"], wt, p + "mix.", eps)
         elif layer["type"] == "attention":
-            x = x + window_attention(h, layer["mixer"], wt, p + "mix.")
+            x = x + window_attention(h, layer["mixer"], wt, p + "mix.", window_delta, keep_delta)
         elif layer["type"] == "mamba2":
             x = x + mamba2(h, layer["mixer"], wt, p + "mix.", eps)
         else:
@@ -205,3 +210,24 @@ def forward(config: dict, weights: dict, tokens, want_layers: bool = False, choi
     if want_layers:
         return logits, after, seen
     return logits
+
+
+def load_folder(model_dir):
+    import json
+    import os
+
+    from safetensors.torch import load_file
+    with open(os.path.join(model_dir, "config.json")) as fh:
+        cfg = json.load(fh)
+    w = {k: (v.to(F64) if v.is_floating_point() else v) for k, v in
+         load_file(os.path.join(model_dir, "model.safetensors")).items()}
+    return cfg, w
+
+
+def generate_greedy(config, W, prompt, n):
+    toks, out = list(prompt), []
+    for _ in range(n):
+        nxt = int(torch.argmax(forward(config, W, toks)[-1]))
+        out.append(nxt)
+        toks.append(nxt)
+    return out
