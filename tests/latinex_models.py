@@ -102,12 +102,26 @@ CASES = {"A": (CASE_A, 0.15, 41), "B": (CASE_B, 0.18, 42), "C": (CASE_C, 0.1, 43
          "E": (CASE_E, 0.1, 45)}
 
 
+def one_layer(name: str, index: int, mlp="same") -> dict:
+    """A case's configuration cut down to one of its layers (``mlp``: the layer's own, or a replacement)."""
+    cfg = dict(CASES[name][0])
+    layer = dict(cfg["layers"][index])
+    if mlp != "same":
+        layer["mlp"] = mlp
+    cfg["layers"] = [layer]
+    return cfg
+
+
 def write(name: str, out_dir: str) -> str:
     """``config.json`` and ``model.safetensors`` for a case: seeded random weights, then the edits named above."""
+    cfg, std, seed = CASES[name]
+    return write_config(cfg, std, seed, out_dir)
+
+
+def write_config(cfg: dict, std: float, seed: int, out_dir: str) -> str:
     from safetensors.torch import load_file
 
     from sharpinference_b200.weights import safetensors_io, write_random_model
-    cfg, std, seed = CASES[name]
     write_random_model(dict(cfg), out_dir, seed, std=std, norm_std=0.1)
     path = os.path.join(out_dir, "model.safetensors")
     tensors = load_file(path)
