@@ -289,6 +289,67 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
                                             float(scale), _stream()), "sharpi_attention_decode")
 
 
+KEYS_ATTENTION_TILE = 64
+
+
+def keys_attention_supported(dtype: torch.dtype, d: int, dv: int) -> bool:
+    """Whether the tensor-core kernels for keys-only pages take a cached row of ``d`` elements of which the first
+    ``dv`` are the value: bfloat16, both multiples of 16, ``dv <= d <= 512``."""
+    return dtype == torch.bfloat16 and d % 16 == 0 and dv % 16 == 0 and 0 < dv <= d <= 512
+
+
+def attention_keys_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor,
+                           out: torch.Tensor, *, nq: int, nkv: int, d: int, dv: int, page_size: int, mask_kind: int,
+                           mask_span: int, scale: float, keep_first: int = 0,
+                           dist_bias: Optional[torch.Tensor] = None) -> None:
+    """Paged attention over keys-only pages ``[pages, 1, nkv, page_size, d]`` for tiles of up to 64 consecutive rows of
+    one request (bfloat16): a key's value is the first ``dv`` elements of its row; ``out`` is ``[T, nq * dv]``.
+    ``keep_first`` and ``dist_bias`` as in :func:`paged_attention_generic`."""
+    _need(q, "q", torch.bfloat16)
+    _need(kv_layer, "kv_layer", torch.bfloat16)
+    _need(out, "out", torch.bfloat16)
+    _need(tiles, "tiles", torch.int32)
+    if not keys_attention_supported(q.dtype, d, dv) or tuple(kv_layer.shape[1:]) != (1, nkv, page_size, d):
+        raise KernelError(f"kv_layer {tuple(kv_layer.shape)} is not [pages, 1, {nkv}, {page_size}, {d}] or the sizes "
+                          f"({d}, {dv}) are no multiples of 16 up to 512")
+    if dist_bias is not None:
+        _need(dist_bias, "dist_bias", torch.float32)
+        if dist_bias.dim() != 2 or dist_bias.shape[1] != nq:
+            raise KernelError(f"dist_bias is {tuple(dist_bias.shape)}, expected [far + 1, {nq}]")
+    check(kernel("sharpi_attention_keys_prefill")(q.data_ptr(), kv_layer.data_ptr(), block_table.data_ptr(), tiles.data_ptr(),
+                                                  out.data_ptr(), tiles.shape[0], nq, nkv, d, dv, block_table.shape[-1],
+                                                  page_size, mask_kind, mask_span, int(keep_first), _ptr(dist_bias),
+                                                  0 if dist_bias is None else dist_bias.shape[0] - 1, float(scale),
+                                                  _stream()), "sharpi_attention_keys_prefill")
+
+
+def attention_keys_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, row_req: torch.Tensor,
+                          positions: torch.Tensor, out: torch.Tensor, *, rows: Optional[torch.Tensor], num_rows: int,
+                          nq: int, nkv: int, d: int, dv: int, page_size: int, mask_kind: int, mask_span: int, scale: float,
+                          max_context: int, keep_first: int = 0, dist_bias: Optional[torch.Tensor] = None) -> None:
+    """The same attention for rows that bring one query each, split over the keys in 256s; ``max_context`` bounds the
+    longest row (position + 1).  Results go to ``out[row]`` (``[T, nq * dv]``)."""
+    _need(q, "q", torch.bfloat16)
+    _need(kv_layer, "kv_layer", torch.bfloat16)
+    _need(out, "out", torch.bfloat16)
+    if not keys_attention_supported(q.dtype, d, dv) or tuple(kv_layer.shape[1:]) != (1, nkv, page_size, d):
+        raise KernelError(f"kv_layer {tuple(kv_layer.shape)} is not [pages, 1, {nkv}, {page_size}, {d}] or the sizes "
+                          f"({d}, {dv}) are no multiples of 16 up to 512")
+    if dist_bias is not None:
+        _need(dist_bias, "dist_bias", torch.float32)
+        if dist_bias.dim() != 2 or dist_bias.shape[1] != nq:
+            raise KernelError(f"dist_bias is {tuple(dist_bias.shape)}, expected [far + 1, {nq}]")
+    splits = max(1, (max_context + DECODE_SPLIT - 1) // DECODE_SPLIT)
+    part_o = torch.empty((num_rows, nq, splits, dv), dtype=torch.float32, device=q.device)
+    part_ml = torch.empty((num_rows, nq, splits, 2), dtype=torch.float32, device=q.device)
+    check(kernel("sharpi_attention_keys_decode")(q.data_ptr(), kv_layer.data_ptr(), block_table.data_ptr(), row_req.data_ptr(),
+                                                 positions.data_ptr(), _ptr(rows), part_o.data_ptr(), part_ml.data_ptr(),
+                                                 out.data_ptr(), num_rows, nq, nkv, d, dv, block_table.shape[-1], page_size,
+                                                 mask_kind, mask_span, int(keep_first), _ptr(dist_bias),
+                                                 0 if dist_bias is None else dist_bias.shape[0] - 1, splits, float(scale),
+                                                 _stream()), "sharpi_attention_keys_decode")
+
+
 def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor,
                       out: torch.Tensor, *, nq: int, nkv: int, d: int, page_size: int, mask_kind: int,
                       mask_span: int, scale: float) -> None:

@@ -259,6 +259,8 @@ class PagedAttention(Mixer):
     def prefill_tile_rows(self, page_size: int) -> int:
         """Rows of one request that one attention CTA serves in a prompt portion: 128 where the tcgen05
         kernel takes this layer (bfloat16, head size 64 or 128, pages of 64 * 2^k), else 64."""
+        if self._general_attention:
+            return ops.KEYS_ATTENTION_TILE
         return ops.TC_PREFILL_TILE if ops.tc_prefill_supported(self.act_dtype, self.head_dim, page_size) else 64
 
     def step_planner(self, page_size: int) -> StepPlanner:
@@ -357,6 +359,16 @@ class PagedAttention(Mixer):
                                      num_rows=plan.num_decode_rows, nq=nq, nkv=nkv, d=d, page_size=slot.page_size,
                                      mask_kind=mask_kind, mask_span=mask_span, scale=self.softmax_scale,
                                      max_context=ctx.max_context, max_keys=plan.decode_keys)
+        elif self.values_are_keys and ops.keys_attention_supported(self.act_dtype, d, d):
+            # keys-only pages: the tensor-core kernels that read a key once for scores and value sum
+            o = torch.empty((T, nq * d), dtype=torch.bfloat16, device=h.device)
+            kw = dict(nq=nq, nkv=nkv, d=d, dv=d, page_size=slot.page_size, mask_kind=mask_kind, mask_span=mask_span,
+                      scale=self.softmax_scale, keep_first=self.keep_first, dist_bias=self.distance_bias)
+            if plan.num_tiles:
+                ops.attention_keys_prefill(q, slot.kv, table, plan.tiles, o, **kw)
+            if plan.num_decode_rows:
+                ops.attention_keys_decode(q, slot.kv, table, ctx.row_request, ctx.positions, o, rows=plan.decode_rows,
+                                          num_rows=plan.num_decode_rows, max_context=ctx.max_context, **kw)
         else:
             o = ops.paged_attention_generic(q, slot.kv, table, ctx.row_request, ctx.positions, nq=nq, nkv=nkv, d=d,
                                             page_size=slot.page_size, mask_kind=mask_kind, mask_span=mask_span,

@@ -74,15 +74,15 @@ class LatentAttention(Mixer):
         self.softmax_scale, self.act_dtype = float(softmax_scale), act_dtype
         # one cached row a token: [c | k_rot], padded to what the attention kernels take as a head size
         D = kv_rank + rot_dim
-        D = (D + 15) // 16 * 16 if D <= 128 else D + (D & 1)
         if D > 512:
             raise ValueError(f"kv_rank + rot_dim = {kv_rank + rot_dim} exceeds the largest head size of the attention "
                              f"kernels (512)")
+        D = (D + 15) // 16 * 16                   # a multiple of 16: the size the tensor-core kernels take
         self.head_dim = D
         self.cache_spec = CacheSpec("full", 0, 1, D, planes=1)
 
     def step_planner(self, page_size: int):
-        return PagedAttentionPlanner(64)
+        return PagedAttentionPlanner(ops.KEYS_ATTENTION_TILE)
 
     def forward(self, ctx: StepContext, slot: LayerSlot, h: torch.Tensor) -> torch.Tensor:
         T, H, D, act = ctx.num_tokens, self.num_heads, self.head_dim, self.act_dtype
@@ -98,9 +98,23 @@ class LatentAttention(Mixer):
         qa = self.up_k.per_group(q_plain, T)                                  # [H T, kv_rank] float32
         qj = ops.latent_q_join(qa, q, ctx.positions, self.inv_freq, heads=H, dim=self.dim, rank=self.kv_rank,
                                rot=self.rot_dim, rot_dims=self.rot_dims, D=D, out_dtype=act)
-        o = ops.paged_attention_generic(qj, slot.kv, table, ctx.row_request, ctx.positions, nq=H, nkv=1, d=D,
-                                        page_size=slot.page_size, mask_kind=ops.MASK_FULL, mask_span=1,
-                                        scale=self.softmax_scale)
-        o_lat = ops.head_major(o, heads=H, stride=D, col0=0, n=self.kv_rank, out_dtype=act)
+        dv = (self.kv_rank + 15) // 16 * 16
+        if ops.keys_attention_supported(act, D, dv) and slot.kv.shape[1] == 1:
+            # the tensor-core kernels for keys-only pages: the value sum is taken over the latent's columns only
+            plan = ctx.plans[("paged_attention", ops.KEYS_ATTENTION_TILE)]
+            o = torch.empty((T, H * dv), dtype=torch.bfloat16, device=h.device)
+            kw = dict(nq=H, nkv=1, d=D, dv=dv, page_size=slot.page_size, mask_kind=ops.MASK_FULL, mask_span=1,
+                      scale=self.softmax_scale)
+            if plan.num_tiles:
+                ops.attention_keys_prefill(qj, slot.kv, table, plan.tiles, o, **kw)
+            if plan.num_decode_rows:
+                ops.attention_keys_decode(qj, slot.kv, table, ctx.row_request, ctx.positions, o, rows=plan.decode_rows,
+                                          num_rows=plan.num_decode_rows, max_context=ctx.max_context, **kw)
+            o_lat = ops.head_major(o, heads=H, stride=dv, col0=0, n=self.kv_rank, out_dtype=act)
+        else:
+            o = ops.paged_attention_generic(qj, slot.kv, table, ctx.row_request, ctx.positions, nq=H, nkv=1, d=D,
+                                            page_size=slot.page_size, mask_kind=ops.MASK_FULL, mask_span=1,
+                                            scale=self.softmax_scale)
+            o_lat = ops.head_major(o, heads=H, stride=D, col0=0, n=self.kv_rank, out_dtype=act)
         v = self.up_v.per_group(o_lat, T)                                     # [H T, value_dim] float32
         return self.out(ops.head_minor(v, heads=H, out_dtype=act))

@@ -285,6 +285,76 @@ def test_keys_as_values_attention_with_one_key_that_stands_out(window, keep, pag
             one = ops.paged_attention_generic(q[row:row + 1].to(dtype).to(DEV).view(1, nq * d), kv, bt, rr[:1],
                                               pos[row:row + 1].contiguous(), **kw)
             assert float((one.double().cpu().view(nq, d) - want[row]).abs().max()) < tol, (j, row, "single row")
+        if dtype == torch.bfloat16:
+            # the tensor-core kernels for keys-only pages: tiles of 64 rows, and single rows split over their keys
+            kw.pop("d")
+            qd = q.to(dtype).to(DEV).view(T, nq * d)
+            tiles = torch.tensor([[t0, min(64, T - t0), t0, 0] for t0 in range(0, T, 64)], dtype=torch.int32, device=DEV)
+            out = torch.zeros(T, nq * d, dtype=dtype, device=DEV)
+            ops.attention_keys_prefill(qd, kv, bt, tiles, out, d=d, dv=d, **kw)
+            assert float((out.double().cpu().view(T, nq, d) - want).abs().max()) < tol, (j, "prompt, tensor cores")
+            some = torch.tensor(sorted({i, j, min(j + window, i), max(min(j + window, i) - 1, 0), 17, 255, 256}),
+                                dtype=torch.int32, device=DEV)
+            out = torch.zeros(T, nq * d, dtype=dtype, device=DEV)
+            ops.attention_keys_decode(qd, kv, bt, rr, pos, out, rows=some, num_rows=some.numel(), max_context=T, d=d, dv=d, **kw)
+            got = out.double().cpu().view(T, nq, d)[some.cpu().long()]
+            assert float((got - want[some.cpu().long()]).abs().max()) < tol, (j, "single rows, tensor cores")
+
+
+@pytest.mark.parametrize("nq,nkv,d,dv,page", [(16, 1, 320, 256, 64), (4, 1, 48, 48, 16), (8, 1, 96, 64, 64), (2, 2, 512, 512, 64),
+                                              (20, 1, 128, 128, 64), (3, 3, 16, 16, 16), (6, 2, 208, 144, 32)])
+def test_tensor_core_attention_over_keys_only_pages(nq, nkv, d, dv, page):
+    """Rows of many sizes whose leading ``dv`` elements are the value: two requests on shuffled pages, portions as
+    tiles and single rows in one step, against the plain softmax."""
+    from sharpinference_b200.kernels import ops
+    g = torch.Generator().manual_seed(nq * d + dv)
+    lens, scale = (333, 70), 2.0 / math.sqrt(d)
+    keys = [torch.randn(n, nkv, d, generator=g).to(torch.bfloat16) for n in lens]
+    qs = [torch.randn(n, nq, d, generator=g).to(torch.bfloat16) for n in lens]
+    want = []
+    for k, q in zip(keys, qs):
+        w = torch.empty(k.shape[0], nq, dv, dtype=F64)
+        for h in range(nq):
+            kh = k[:, h // (nq // nkv)].double()
+            w[:, h] = plain.softmax_rows(q[:, h].double() @ kh.T * scale, plain.causal(k.shape[0])) @ kh[:, :dv]
+        want.append(w)
+    blocks = [(n + page - 1) // page for n in lens]
+    pool = sum(blocks) + 3
+    perm = torch.randperm(pool, generator=g)
+    kv = torch.full((pool, 1, nkv, page, d), 30.0).to(torch.bfloat16)
+    bt = torch.full((2, max(blocks)), -1, dtype=torch.int32)
+    at = 0
+    for b, k in enumerate(keys):
+        for blk in range(blocks[b]):
+            pg = int(perm[at])
+            at += 1
+            bt[b, blk] = pg
+            rows = k[blk * page:(blk + 1) * page]
+            kv[pg, 0, :, :rows.shape[0]] = rows.transpose(0, 1)
+    kv, bt = kv.to(DEV), bt.to(DEV)
+    # one step: request 0 brings its rows 100 .. 332 (a portion: tiles), request 1 its last three rows (single rows)
+    step_rows = [(0, r) for r in range(100, 333)] + [(1, r) for r in range(67, 70)]
+    q = torch.stack([qs[b][r] for b, r in step_rows]).to(DEV).view(len(step_rows), nq * d)
+    rr = torch.tensor([b for b, _ in step_rows], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([r for _, r in step_rows], dtype=torch.int32, device=DEV)
+    tiles = torch.tensor([[t0, min(64, 233 - t0), 100 + t0, 0] for t0 in range(0, 233, 64)], dtype=torch.int32, device=DEV)
+    single = torch.tensor([233, 234, 235], dtype=torch.int32, device=DEV)
+    out = torch.zeros(len(step_rows), nq * dv, dtype=torch.bfloat16, device=DEV)
+    kw = dict(nq=nq, nkv=nkv, d=d, dv=dv, page_size=page, mask_kind=ops.MASK_FULL, mask_span=1, scale=scale)
+    ops.attention_keys_prefill(q, kv, bt, tiles, out, **kw)
+    ops.attention_keys_decode(q, kv, bt, rr, pos, out, rows=single, num_rows=3, max_context=333, **kw)
+    got = out.double().cpu().view(len(step_rows), nq, dv)
+    ref = torch.stack([want[b][r] for b, r in step_rows])
+    assert float((got - ref).abs().max()) < 3e-2
+    # a row alone gives the bits it gave in the batch, and a row of a tile the bits of the same row in a tile cut elsewhere
+    alone = torch.zeros_like(out)
+    ops.attention_keys_decode(q, kv, bt, rr, pos, alone, rows=single[1:2].contiguous(), num_rows=1, max_context=70, **kw)
+    assert torch.equal(alone[234], out[234])
+    other = torch.zeros_like(out)
+    tiles2 = torch.tensor([[0, 7, 100, 0], [7, 64, 107, 0], [71, 64, 171, 0], [135, 64, 235, 0], [199, 34, 299, 0]],
+                          dtype=torch.int32, device=DEV)
+    ops.attention_keys_prefill(q, kv, bt, tiles2, other, **kw)
+    assert torch.equal(other[:233], out[:233])
 
 
 def test_distance_bias_is_not_scaled_and_reads_the_head_of_the_query():
