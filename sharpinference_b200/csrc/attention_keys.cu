@@ -44,22 +44,29 @@ struct KeysArgs {
     float* part_o;            // decode: [R, nq, max_splits, dv]
     float* part_ml;           // decode: [R, nq, max_splits, 2]   (max in log2 units, sum)
     bf16* out;                // [T, nq, dv]
-    int nq, nkv, D, dv, ld, max_blocks, page_size, mask_kind, mask_span, keep_first, dist_far, max_splits;
+    int nq, nkv, D, dv, ld, max_blocks, page_size, page_shift, mask_kind, mask_span, keep_first, dist_far, max_splits;
     float scale_log2;
 };
 
+// One block of 64 keys into shared memory: a warp takes every n-th row (one look at the block table a row), its lanes
+// the row's 16-byte pieces, so that no address needs a division by a run-time size.
 __device__ __forceinline__ void keys_load_block(const KeysArgs& a, const int* table, int kvh, int key0, int key_hi,
                                                 bf16* k_s) {
-    const int vec = a.D / 8;
-    for (int idx = threadIdx.x; idx < KA_BK * vec; idx += KA_THREADS) {
-        const int row = idx / vec, col = idx % vec;
+    const int vec = a.D >> 3;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    for (int row = warp; row < KA_BK; row += n_warps) {
         const int key = key0 + row;
         bool valid = key <= key_hi;
-        const int page = valid ? table[key / a.page_size] : -1;
+        int page = -1, off = 0;
+        if (valid) {
+            const int blk = a.page_shift >= 0 ? (key >> a.page_shift) : (key / a.page_size);
+            off = key - blk * a.page_size;
+            page = table[blk];
+        }
         valid = valid && page >= 0;
-        const bf16* src = a.kv;
-        if (valid) src = a.kv + ((size_t)page * a.nkv + kvh) * a.page_size * a.D + (size_t)(key % a.page_size) * a.D + col * 8;
-        cp_async_16(k_s + row * a.ld + col * 8, src, valid ? 16 : 0);
+        const bf16* src = valid ? a.kv + (((size_t)page * a.nkv + kvh) * a.page_size + off) * a.D : a.kv;
+        bf16* dst = k_s + row * a.ld;
+        for (int c = lane; c < vec; c += 32) cp_async_16(dst + c * 8, valid ? src + c * 8 : src, valid ? 16 : 0);
     }
 }
 
@@ -142,21 +149,24 @@ __device__ __forceinline__ void keys_scores(float (&s)[NT][4], const bf16* q_s, 
     }
 }
 
-template <int NV>     // value columns a CTA: 16 NV
-__global__ void __launch_bounds__(KA_THREADS) keys_prefill_kernel(KeysArgs a) {
+template <int NV, int HPC>     // value columns a CTA: 16 NV; query heads a CTA (of one key head): four warps each
+__global__ void __launch_bounds__(KA_THREADS * HPC) keys_prefill_kernel(KeysArgs a) {
     extern __shared__ __align__(16) uint8_t smem_bytes[];
     const int ld = a.ld;
-    bf16* q_s = reinterpret_cast<bf16*>(smem_bytes);      // [64][ld]
-    bf16* kv_s = q_s + KA_BQ * ld;                          // [2 stages][64][ld]
-    float* bias_s = reinterpret_cast<float*>(kv_s + 2 * KA_BK * ld);     // [dist_far + 1]: this head's column
+    bf16* q_s = reinterpret_cast<bf16*>(smem_bytes);      // [HPC][64][ld]
+    bf16* kv_s = q_s + HPC * KA_BQ * ld;                    // [2 stages][64][ld]
+    float* bias_s = reinterpret_cast<float*>(kv_s + 2 * KA_BK * ld);     // [HPC][dist_far + 1]: the heads' columns
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = (threadIdx.x >> 5) % 4, lane = threadIdx.x & 31, hi = threadIdx.x / KA_THREADS;
     const int* tile = a.tiles + (size_t)(gridDim.y - 1 - blockIdx.y) * 4;      // the tiles with the most keys first
     const int row0 = tile[0], n_rows = tile[1], p0 = tile[2];
     const int* table = a.block_table + (size_t)tile[3] * a.max_blocks;
-    const int head = blockIdx.x;
+    const int head = blockIdx.x * HPC + hi;
     const int kvh = head / (a.nq / a.nkv);
     const int vcol0 = blockIdx.z * (16 * NV);
+    q_s += hi * KA_BQ * ld;
+    bias_s += hi * (a.dist_far + 1);
+    const int tid = threadIdx.x % KA_THREADS;
 
     const int p_last = p0 + n_rows - 1;
     const int key_lo = visible_lo(p0, a.mask_kind, a.mask_span);
@@ -168,16 +178,15 @@ __global__ void __launch_bounds__(KA_THREADS) keys_prefill_kernel(KeysArgs a) {
     auto block_of = [&](int it) { return it < n_keep ? it : kb_first + (it - n_keep); };
 
     const int vec = a.D / 8;
-    for (int idx = threadIdx.x; idx < KA_BQ * vec; idx += KA_THREADS) {
-        const int r = idx / vec, c = idx % vec;
+    for (int r = warp; r < KA_BQ; r += 4) {
         const bool valid = r < n_rows;
-        const bf16* src = valid ? a.q + ((size_t)(row0 + r) * a.nq + head) * a.D + c * 8 : a.q;
-        cp_async_16(q_s + r * ld + c * 8, src, valid ? 16 : 0);
+        const bf16* src = valid ? a.q + ((size_t)(row0 + r) * a.nq + head) * a.D : a.q;
+        for (int c = lane; c < vec; c += 32) cp_async_16(q_s + r * ld + c * 8, valid ? src + c * 8 : src, valid ? 16 : 0);
     }
     keys_load_block(a, table, kvh, block_of(0) * KA_BK, p_last, kv_s);
     cp_async_commit();
     if (a.dist_bias != nullptr)
-        for (int i = threadIdx.x; i <= a.dist_far; i += KA_THREADS) bias_s[i] = a.dist_bias[(size_t)i * a.nq + head];
+        for (int i = tid; i <= a.dist_far; i += KA_THREADS) bias_s[i] = a.dist_bias[(size_t)i * a.nq + head];
 
     float o[2 * NV][4];
 #pragma unroll
@@ -425,6 +434,9 @@ static bool keys_fill(KeysArgs& a, const void* q, const void* kv, const int* blo
     a.dist_bias = dist_bias; a.nq = nq; a.nkv = nkv; a.D = D; a.dv = dv; a.max_blocks = max_blocks; a.page_size = page_size;
     a.mask_kind = mask_kind; a.mask_span = mask_span; a.keep_first = keep_first; a.dist_far = dist_bias ? dist_far : 0;
     a.max_splits = 0; a.scale_log2 = scale * KA_LOG2E;
+    a.page_shift = -1;
+    for (int sft = 0; sft < 31; ++sft)
+        if ((1 << sft) == page_size) a.page_shift = sft;
     *nv = dv <= 16 ? 1 : dv <= 32 ? 2 : dv <= 64 ? 4 : dv <= 128 ? 8 : 16;
     *n_chunks = (dv + 16 * *nv - 1) / (16 * *nv);
     const int cols = *n_chunks * 16 * *nv;
@@ -432,19 +444,27 @@ static bool keys_fill(KeysArgs& a, const void* q, const void* kv, const int* blo
     return true;
 }
 
-template <int NV>
-static int keys_launch_prefill(const KeysArgs& a, int n_tiles, int n_chunks, cudaStream_t stream) {
-    const size_t smem = (size_t)3 * KA_BK * a.ld * 2 + (size_t)(a.dist_far + 1) * 4;
-    if (smem > 227 * 1024) return SHARPI_BAD_ARGUMENT;
+template <int NV, int HPC>
+static int keys_launch_prefill_h(const KeysArgs& a, int n_tiles, int n_chunks, size_t smem, cudaStream_t stream) {
     static size_t configured = 0;
     if (smem > configured) {
-        if (cudaFuncSetAttribute(keys_prefill_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(keys_prefill_kernel<NV, HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return SHARPI_LAUNCH_FAILED;
         configured = smem;
     }
-    keys_prefill_kernel<NV><<<dim3(a.nq, n_tiles, n_chunks), KA_THREADS, smem, stream>>>(a);
+    keys_prefill_kernel<NV, HPC><<<dim3(a.nq / HPC, n_tiles, n_chunks), KA_THREADS * HPC, smem, stream>>>(a);
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
+}
+
+// Two heads of one key head share a CTA (and its key blocks) where there are two and shared memory holds both query tiles.
+template <int NV>
+static int keys_launch_prefill(const KeysArgs& a, int n_tiles, int n_chunks, cudaStream_t stream) {
+    const size_t bias = (size_t)(a.dist_far + 1) * 4;
+    const size_t one = (size_t)3 * KA_BK * a.ld * 2 + bias, two = (size_t)4 * KA_BK * a.ld * 2 + 2 * bias;
+    if (one > 227 * 1024) return SHARPI_BAD_ARGUMENT;
+    if ((a.nq / a.nkv) % 2 == 0 && two <= 227 * 1024) return keys_launch_prefill_h<NV, 2>(a, n_tiles, n_chunks, two, stream);
+    return keys_launch_prefill_h<NV, 1>(a, n_tiles, n_chunks, one, stream);
 }
 
 template <int NV>
