@@ -369,7 +369,7 @@ def main() -> int:
     prefill = {"value": ns.prefill_tokens / pre * 1e3, "tokens": ns.prefill_tokens, "ms": pre,
                "frac": prefill_flops(cfg, ns.prefill_tokens) / (pre * 1e-3) / (pk["bf16_tflops"] * 1e12),
                "peak_tflops": pk["bf16_tflops"], "peak": pk_kind,
-               # beside the contract's flops fraction: against the step's own floor, whose routed experts are
+               # beside the headline flops fraction: against the step's own floor, whose routed experts are
                # bound by the bytes of their weights
                "floor_ms": prefill_floor_ms(cfg, ns.prefill_tokens, pk)}
     prefill["frac_of_floor"] = prefill["floor_ms"] / pre

@@ -12,6 +12,9 @@
     python bench_kernels.py scan --batch 64 --tokens 1             (convolution and selective scan)
     python bench_kernels.py streams --tokens 2048                  (stream update + grouped norm, token shift)
     python bench_kernels.py mixture_glue --tokens 2048             (activation, pair rows, combine)
+    python bench_kernels.py ssd --batch 64 --tokens 1              (state-space duality and its gated norm)
+    python bench_kernels.py attention_keys_decode --batch 64 --context 8192     (keys-only pages)
+    python bench_kernels.py attention_keys_prefill --tokens 2048 --mask window
 
 Each run warms the kernel up, times ``--iters`` launches with CUDA events and prints one line with
 the time per launch and the achieved bytes or flops per second.  The inputs are larger than the L2
@@ -412,6 +415,86 @@ def attention_prefill(ns) -> None:
     print(f"attention_prefill ({'m16n8k16' if ns.warp_mma else 'tcgen05'}) tokens={T} start={start} heads={nq}/{nkv} d={d}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.0f} TFLOP/s")
 
 
+def ssd(ns) -> None:
+    """The state-space-duality recurrence and the gated group norm behind it for `batch` requests of `tokens` rows
+    each: per row and head 4 states x vdim flops (decay and update of S, S^T C); decode streams the state once."""
+    B, n, heads, N, P = ns.batch, ns.tokens, ns.heads, ns.states, ns.value_dim
+    T, inner = B * n, heads * P
+    xbc = 0.5 * torch.randn(T, inner + 2 * N, device=DEV)
+    proj = torch.randn(T, 2 * inner + 2 * N + heads, device=DEV)         # [x B C | z | dt], as the mixer lays it out
+    col_z, col_dt = inner + 2 * N, 2 * inner + 2 * N
+    dt_bias, a_log, dsk = torch.zeros(heads, device=DEV), torch.zeros(heads, device=DEV), torch.ones(heads, device=DEV)
+    w = torch.ones(inner, device=DEV)
+    per_request = heads * N * P
+    copies = max(1, (300 << 20) // (B * per_request * 4) + 1) if n == 1 else 1
+    state = torch.zeros(copies * B, per_request, device=DEV)
+    offs = torch.arange(0, T + 1, n, dtype=torch.int32, device=DEV)
+    slot_sets = [torch.arange(c * B, (c + 1) * B, dtype=torch.int32, device=DEV) for c in range(copies)]
+    it = {"i": 0}
+
+    def fn():
+        slots = slot_sets[it["i"] % copies]
+        it["i"] += 1
+        y = ops.ssd_scan(xbc, proj, col_x=0, col_b=inner, col_c=inner + N, col_dt=col_dt, dt_bias=dt_bias, a_log=a_log,
+                         dskip=dsk, row_offsets=offs, state_slots=slots, state=state, heads=heads, groups=1, states=N, vdim=P)
+        ops.gated_group_norm(y, proj, col_z, w, 1e-5, 1, torch.bfloat16)
+    ms = _time(fn, max(ns.iters, copies))
+    print(f"ssd batch={B} tokens={n} heads={heads} states={N} vdim={P}: {ms * 1e3:.1f} us, state {2 * B * per_request * 4 / ms / 1e6:.0f} GB/s "
+          f"(read and written once), {4.0 * T * per_request / ms / 1e9:.2f} TFLOP/s float32")
+
+
+def _keys_cache(batch: int, context: int, nkv: int, d: int, ps: int):
+    blocks = (context + ps - 1) // ps
+    pages = batch * blocks
+    kv = torch.empty(pages, 1, nkv, ps, d, dtype=torch.bfloat16, device=DEV).normal_(0, 1)
+    table = torch.randperm(pages, device=DEV).to(torch.int32).view(batch, blocks).contiguous()
+    return kv, table
+
+
+def _keys_mask(ns):
+    kind = {"full": ops.MASK_FULL, "window": ops.MASK_WINDOW}[ns.mask]
+    bias = 0.1 * torch.randn(ns.bias_far + 1, ns.heads, device=DEV) if ns.bias_far else None
+    return kind, bias
+
+
+def _visible(pos: int, kind: int, span: int, keep: int) -> int:
+    return pos + 1 if kind == ops.MASK_FULL or pos < span else span + min(keep, pos + 1 - span)
+
+
+def attention_keys_decode(ns) -> None:
+    """Single query rows over keys-only pages (a key's leading elements are its value): the keys stream once."""
+    B, S, nq, nkv, d, dv, ps = ns.batch, ns.context, ns.heads, ns.kv_heads, ns.head_dim, ns.value_dim or ns.head_dim, ns.page_size
+    kv, table = _keys_cache(B, S, nkv, d, ps)
+    q = torch.randn(B, nq, d, device=DEV).to(torch.bfloat16)
+    positions = torch.full((B,), S - 1, dtype=torch.int32, device=DEV)
+    row_req = torch.arange(B, dtype=torch.int32, device=DEV)
+    out = torch.empty(B, nq * dv, dtype=torch.bfloat16, device=DEV)
+    kind, bias = _keys_mask(ns)
+    fn = lambda: ops.attention_keys_decode(q, kv, table, row_req, positions, out, rows=None, num_rows=B, nq=nq, nkv=nkv, d=d,
+                                           dv=dv, page_size=ps, mask_kind=kind, mask_span=ns.span, scale=1 / math.sqrt(d),
+                                           max_context=S, keep_first=ns.keep_first, dist_bias=bias)
+    ms = _time(fn, ns.iters)
+    nbytes = B * _visible(S - 1, kind, ns.span, ns.keep_first) * nkv * d * 2
+    print(f"attention_keys_decode batch={B} context={S} heads={nq}/{nkv} d={d} dv={dv} mask={ns.mask}: {ms * 1e3:.1f} us, "
+          f"{nbytes / ms / 1e6:.0f} GB/s of visible keys")
+
+
+def attention_keys_prefill(ns) -> None:
+    """One prompt of `tokens` rows over keys-only pages in tiles of 64 rows: 2 (d + dv) flops a (query, visible key)."""
+    T, nq, nkv, d, dv, ps = ns.tokens, ns.heads, ns.kv_heads, ns.head_dim, ns.value_dim or ns.head_dim, ns.page_size
+    kv, table = _keys_cache(1, T, nkv, d, ps)
+    q = torch.randn(T, nq, d, device=DEV).to(torch.bfloat16)
+    tiles = torch.tensor([[t0, min(64, T - t0), t0, 0] for t0 in range(0, T, 64)], dtype=torch.int32, device=DEV)
+    out = torch.empty(T, nq * dv, dtype=torch.bfloat16, device=DEV)
+    kind, bias = _keys_mask(ns)
+    fn = lambda: ops.attention_keys_prefill(q, kv, table, tiles, out, nq=nq, nkv=nkv, d=d, dv=dv, page_size=ps, mask_kind=kind,
+                                            mask_span=ns.span, scale=1 / math.sqrt(d), keep_first=ns.keep_first, dist_bias=bias)
+    ms = _time(fn, ns.iters)
+    pairs = sum(_visible(t, kind, ns.span, ns.keep_first) for t in range(T))
+    print(f"attention_keys_prefill tokens={T} heads={nq}/{nkv} d={d} dv={dv} mask={ns.mask}: {ms * 1e3:.1f} us, "
+          f"{2.0 * (d + dv) * nq * pairs / ms / 1e9:.0f} TFLOP/s")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="kernel", required=True)
@@ -503,6 +586,28 @@ def main(argv=None) -> int:
         p.add_argument("--mask", choices=["full", "chunk", "window"], default="full")
         p.add_argument("--span", type=int, default=8192)
         p.add_argument("--warp-mma", action="store_true", help="attention_prefill: the m16n8k16 kernel with 64-row tiles")
+        p.set_defaults(fn=fn)
+    p = sub.add_parser("ssd")
+    p.add_argument("--batch", type=int, default=64)
+    p.add_argument("--tokens", type=int, default=1)
+    p.add_argument("--heads", type=int, default=64)
+    p.add_argument("--states", type=int, default=128)
+    p.add_argument("--value-dim", type=int, default=64)
+    p.set_defaults(fn=ssd)
+    for name, fn in (("attention_keys_decode", attention_keys_decode), ("attention_keys_prefill", attention_keys_prefill)):
+        p = sub.add_parser(name)
+        p.add_argument("--batch", type=int, default=8)
+        p.add_argument("--context", type=int, default=8192)
+        p.add_argument("--tokens", type=int, default=2048)
+        p.add_argument("--heads", type=int, default=16)
+        p.add_argument("--kv-heads", type=int, default=4)
+        p.add_argument("--head-dim", type=int, default=128)
+        p.add_argument("--value-dim", type=int, default=0, help="a value's size (the head size when 0)")
+        p.add_argument("--page-size", type=int, default=64)
+        p.add_argument("--mask", choices=["full", "window"], default="full")
+        p.add_argument("--span", type=int, default=1024)
+        p.add_argument("--keep-first", type=int, default=0)
+        p.add_argument("--bias-far", type=int, default=0, help="rows of a distance-bias table minus one (0: no bias)")
         p.set_defaults(fn=fn)
     for sp in sub.choices.values():
         sp.add_argument("--iters", type=int, default=10)
