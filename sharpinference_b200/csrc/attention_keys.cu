@@ -48,25 +48,37 @@ struct KeysArgs {
     float scale_log2;
 };
 
-// One block of 64 keys into shared memory: a warp takes every n-th row (one look at the block table a row), its lanes
-// the row's 16-byte pieces, so that no address needs a division by a run-time size.
+// One block of 64 keys into shared memory.  A warp takes every n-th row.  Its lanes first look up the places of the
+// warp's rows side by side (one wait for the block table a block, not one a row), then hand them round by shuffle;
+// rows of up to 16 pieces of 16 bytes go two at a time, so that every lane copies.  No address needs a division by a
+// run-time size.
 __device__ __forceinline__ void keys_load_block(const KeysArgs& a, const int* table, int kvh, int key0, int key_hi,
                                                 bf16* k_s) {
     const int vec = a.D >> 3;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
-    for (int row = warp; row < KA_BK; row += n_warps) {
-        const int key = key0 + row;
-        bool valid = key <= key_hi;
-        int page = -1, off = 0;
-        if (valid) {
+    const int per_warp = KA_BK / n_warps;             // 16 or 8 rows: warp, warp + n_warps, ...
+    long long my_src = -1;                            // the element offset of row warp + n_warps * lane, -1: no such key
+    if (lane < per_warp) {
+        const int key = key0 + warp + n_warps * lane;
+        if (key <= key_hi) {
             const int blk = a.page_shift >= 0 ? (key >> a.page_shift) : (key / a.page_size);
-            off = key - blk * a.page_size;
-            page = table[blk];
+            const int page = table[blk];
+            if (page >= 0) my_src = (((long long)page * a.nkv + kvh) * a.page_size + (key - blk * a.page_size)) * a.D;
         }
-        valid = valid && page >= 0;
-        const bf16* src = valid ? a.kv + (((size_t)page * a.nkv + kvh) * a.page_size + off) * a.D : a.kv;
-        bf16* dst = k_s + row * a.ld;
-        for (int c = lane; c < vec; c += 32) cp_async_16(dst + c * 8, valid ? src + c * 8 : src, valid ? 16 : 0);
+    }
+    if (vec <= 16) {
+        const int half = lane >> 4, c = lane & 15;
+        for (int i = 0; i < per_warp; i += 2) {
+            const long long src = __shfl_sync(0xffffffffu, my_src, i + half);
+            bf16* dst = k_s + (warp + n_warps * (i + half)) * a.ld;
+            if (c < vec) cp_async_16(dst + c * 8, src >= 0 ? a.kv + src + c * 8 : a.kv, src >= 0 ? 16 : 0);
+        }
+    } else {
+        for (int i = 0; i < per_warp; ++i) {
+            const long long src = __shfl_sync(0xffffffffu, my_src, i);
+            bf16* dst = k_s + (warp + n_warps * i) * a.ld;
+            for (int c = lane; c < vec; c += 32) cp_async_16(dst + c * 8, src >= 0 ? a.kv + src + c * 8 : a.kv, src >= 0 ? 16 : 0);
+        }
     }
 }
 

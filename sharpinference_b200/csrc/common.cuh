@@ -43,6 +43,11 @@ __device__ __forceinline__ void pdl_wait() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+// The wait alone, for a kernel whose few blocks run long (a walk over a prompt's rows): were the next kernel's blocks
+// let onto the SMs meanwhile, the kernel after that would find the SMs unevenly taken and its blocks would land
+// several to an SM.  The next kernel starts when this one has ended.
+__device__ __forceinline__ void pdl_wait_only() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 static int sharpi_pdl_flag = 1;
 static inline int sharpi_pdl_enabled() { return sharpi_pdl_flag; }
 SHARPI_API void sharpi_set_programmatic_launch(int on) { sharpi_pdl_flag = on ? 1 : 0; }

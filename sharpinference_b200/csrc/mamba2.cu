@@ -41,6 +41,7 @@ struct SsdArgs {
     long long state_stride;
     float* y;                // [T, heads * P]
     int heads, groups, N, P;
+    int walk;                // some request brings more than one row: launched the plain way, onto an empty GPU
 };
 
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
@@ -55,7 +56,7 @@ __global__ void __launch_bounds__(SSD_THREADS) ssd_scan_kernel(SsdArgs a) {
     constexpr int STAGE = SSD_CH * (2 * NP + SSD_COLS + 2);      // floats: B, C, x, raw dt then dt, decay
     extern __shared__ __align__(16) float smem[];
     const int N = a.N, P = a.P;
-    pdl_wait();
+    if (a.walk) pdl_wait_only(); else pdl_wait();
     const int req = blockIdx.z, h = blockIdx.y;
     const int g = h / (a.heads / a.groups);
     const int first = a.row_offsets[req], rows = a.row_offsets[req + 1] - first;
@@ -165,7 +166,14 @@ static int ssd_launch(const SsdArgs& a, dim3 grid, cudaStream_t stream) {
         configured = true;
     }
     auto kern = ssd_scan_kernel<NPL>;
-    SHARPI_LAUNCH_PDL(kern, grid, SSD_THREADS, smem, stream, a);
+    if (a.walk) {
+        // a block walks its rows for hundreds of microseconds and there is less than a block an SM: started beside
+        // the tail of the kernel before it, the blocks would share SMs that happened to be free and run at half speed
+        kern<<<grid, SSD_THREADS, smem, stream>>>(a);
+        SHARPI_CHECK_LAUNCH();
+    } else {
+        SHARPI_LAUNCH_PDL(kern, grid, SSD_THREADS, smem, stream, a);
+    }
     return SHARPI_OK;
 }
 
@@ -182,7 +190,7 @@ SHARPI_API int sharpi_ssd_scan(const float* xbc, int ld_x, int col_x, int col_b,
     a.xbc = xbc; a.ld_x = ld_x; a.col_x = col_x; a.col_b = col_b; a.col_c = col_c; a.dt = dt; a.ld_dt = ld_dt;
     a.col_dt = col_dt; a.dt_bias = dt_bias; a.a_log = a_log; a.dskip = dskip; a.row_offsets = row_offsets;
     a.state_slots = state_slots; a.state = state; a.state_stride = state_stride; a.y = y; a.heads = heads;
-    a.groups = groups; a.N = N; a.P = P;
+    a.groups = groups; a.N = N; a.P = P; a.walk = T > B;
     const dim3 grid((P + SSD_COLS - 1) / SSD_COLS, heads, B);
     const int per_lane = (N + SSD_LANES - 1) / SSD_LANES;
     if (per_lane <= 4) return ssd_launch<4>(a, grid, stream);
