@@ -48,18 +48,17 @@ struct KeysArgs {
     float scale_log2;
 };
 
-// One block of 64 keys into shared memory.  A warp takes every n-th row.  Its lanes first look up the places of the
-// warp's rows side by side (one wait for the block table a block, not one a row), then hand them round by shuffle;
-// rows of up to 16 pieces of 16 bytes go two at a time, so that every lane copies.  No address needs a division by a
-// run-time size.
-__device__ __forceinline__ void keys_load_block(const KeysArgs& a, const int* table, int kvh, int key0, int key_hi,
-                                                bf16* k_s) {
+// Rows first, first + step, ... (`count` of them, at most 32) of the keys from key0 on into k_s, by one warp.  Its
+// lanes first look up the places of the rows side by side (one wait for the block table, not one a row), then hand
+// them round by shuffle; rows of up to 16 pieces of 16 bytes go two at a time, so that every lane copies.  No
+// address needs a division by a run-time size.
+__device__ __forceinline__ void keys_load_rows(const KeysArgs& a, const int* table, int kvh, int key0, int key_hi,
+                                               bf16* k_s, int first, int step, int count) {
     const int vec = a.D >> 3;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
-    const int per_warp = KA_BK / n_warps;             // 16 or 8 rows: warp, warp + n_warps, ...
-    long long my_src = -1;                            // the element offset of row warp + n_warps * lane, -1: no such key
-    if (lane < per_warp) {
-        const int key = key0 + warp + n_warps * lane;
+    const int lane = threadIdx.x & 31;
+    long long my_src = -1;                            // the element offset of row first + step * lane, -1: no such key
+    if (lane < count) {
+        const int key = key0 + first + step * lane;
         if (key <= key_hi) {
             const int blk = a.page_shift >= 0 ? (key >> a.page_shift) : (key / a.page_size);
             const int page = table[blk];
@@ -68,18 +67,25 @@ __device__ __forceinline__ void keys_load_block(const KeysArgs& a, const int* ta
     }
     if (vec <= 16) {
         const int half = lane >> 4, c = lane & 15;
-        for (int i = 0; i < per_warp; i += 2) {
+        for (int i = 0; i < count; i += 2) {           // count is even
             const long long src = __shfl_sync(0xffffffffu, my_src, i + half);
-            bf16* dst = k_s + (warp + n_warps * (i + half)) * a.ld;
+            bf16* dst = k_s + (first + step * (i + half)) * a.ld;
             if (c < vec) cp_async_16(dst + c * 8, src >= 0 ? a.kv + src + c * 8 : a.kv, src >= 0 ? 16 : 0);
         }
     } else {
-        for (int i = 0; i < per_warp; ++i) {
+        for (int i = 0; i < count; ++i) {
             const long long src = __shfl_sync(0xffffffffu, my_src, i);
-            bf16* dst = k_s + (warp + n_warps * i) * a.ld;
+            bf16* dst = k_s + (first + step * i) * a.ld;
             for (int c = lane; c < vec; c += 32) cp_async_16(dst + c * 8, src >= 0 ? a.kv + src + c * 8 : a.kv, src >= 0 ? 16 : 0);
         }
     }
+}
+
+// One block of 64 keys into shared memory by all warps of the CTA: a warp takes every n-th row.
+__device__ __forceinline__ void keys_load_block(const KeysArgs& a, const int* table, int kvh, int key0, int key_hi,
+                                                bf16* k_s) {
+    const int n_warps = blockDim.x >> 5;
+    keys_load_rows(a, table, kvh, key0, key_hi, k_s, threadIdx.x >> 5, n_warps, KA_BK / n_warps);
 }
 
 // The scaled, biased and masked scores of one thread's part of a 16 x (8 NT) score tile, the running max and sum,
@@ -272,6 +278,141 @@ __global__ void __launch_bounds__(KA_THREADS * HPC) keys_prefill_kernel(KeysArgs
     }
 }
 
+// The end of a decode CTA: every warp leaves its partial in shared memory (the key blocks are no longer read), then
+// the block adds the four in the order of the warps and writes the split's partial.
+template <int NV>
+__device__ __forceinline__ void keys_decode_finish(const KeysArgs& a, bf16* kv_s, const float (&o)[2 * NV][4],
+                                                   const float (&m_run)[2], const float (&l_run)[2], int heads_here,
+                                                   int head0, int vcol0, int ri, int split, int chunk) {
+    constexpr int DVC = 16 * NV;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* o_w = reinterpret_cast<float*>(kv_s) + (size_t)warp * (16 * DVC + 32);     // [16][DVC] then [16][2]
+    float* ml_w = o_w + 16 * DVC;
+#pragma unroll
+    for (int i = 0; i < 2 * NV; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o_w[(lane / 4 + 8 * (e >> 1)) * DVC + i * 8 + (lane % 4) * 2 + (e & 1)] = o[i][e];
+    if (lane % 4 == 0) {
+        ml_w[(lane / 4) * 2] = m_run[0];
+        ml_w[(lane / 4) * 2 + 1] = l_run[0];
+        ml_w[(lane / 4 + 8) * 2] = m_run[1];
+        ml_w[(lane / 4 + 8) * 2 + 1] = l_run[1];
+    }
+    __syncthreads();
+    const float* base = reinterpret_cast<const float*>(kv_s);
+    constexpr int WS = 16 * DVC + 32;
+    for (int idx = threadIdx.x; idx < heads_here * DVC; idx += KA_THREADS) {
+        const int g = idx / DVC, dd = idx % DVC;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, base[w * WS + 16 * DVC + g * 2]);
+        float acc = 0.0f, L = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = base[w * WS + 16 * DVC + g * 2];
+            const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - M);
+            acc += f * base[w * WS + g * DVC + dd];
+            L += f * base[w * WS + 16 * DVC + g * 2 + 1];
+        }
+        const size_t slot = ((size_t)ri * a.nq + head0 + g) * a.max_splits + split;
+        if (vcol0 + dd < a.dv) a.part_o[slot * a.dv + vcol0 + dd] = acc;
+        if (dd == 0 && chunk == 0) {
+            a.part_ml[slot * 2] = M;
+            a.part_ml[slot * 2 + 1] = L;
+        }
+    }
+}
+
+// The same CTA with a block of 64 keys a warp: every warp asks for its whole block at once, waits once and takes the
+// 64 keys in one pass (one maximum, no correction of earlier sums, the query fragments read once), and nothing but
+// the query tile and the end is shared between the warps.  Shared memory holds the split's 256 keys; sizes that
+// leave room for fewer than two CTAs an SM take keys_decode_kernel.
+template <int NV>
+__global__ void __launch_bounds__(KA_THREADS) keys_decode_warp_kernel(KeysArgs a) {
+    extern __shared__ __align__(16) uint8_t smem_bytes[];
+    const int ld = a.ld;
+    bf16* kv_s = reinterpret_cast<bf16*>(smem_bytes);     // [4 warps][64][ld]; the warps' partials afterwards
+    bf16* q_s = kv_s + 4 * KA_BK * ld;                      // [16][ld]
+    constexpr int DVC = 16 * NV;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_wait();
+    const int G = a.nq / a.nkv;
+    const int groups = (G + 15) / 16;
+    const int n_chunks = gridDim.y / (a.nkv * groups);
+    const int chunk = blockIdx.y % n_chunks;
+    const int kvh = (blockIdx.y / n_chunks) / groups, hg = (blockIdx.y / n_chunks) % groups;
+    const int head0 = kvh * G + hg * 16;
+    const int heads_here = min(16, G - hg * 16);
+    const int vcol0 = chunk * DVC;
+    const int ri = blockIdx.z, split = blockIdx.x;
+    const int r = a.rows ? a.rows[ri] : ri;
+    const int pos = a.positions[r];
+    const int lo = visible_lo(pos, a.mask_kind, a.mask_span);
+    const int keep = a.mask_kind == SHARPI_MASK_WINDOW ? a.keep_first : 0;
+    const int k0 = split * KA_SPLIT;
+    if (k0 > pos) return;                                     // the merge reads the splits up to pos / 256 only
+    const int k1 = min(pos, k0 + KA_SPLIT - 1);
+    if (k1 < lo && k0 >= keep) {                              // a split wholly behind the window: an empty partial
+        if (chunk == 0 && threadIdx.x < heads_here) {
+            const size_t slot = ((size_t)ri * a.nq + head0 + threadIdx.x) * a.max_splits + split;
+            a.part_ml[slot * 2] = -INFINITY;
+            a.part_ml[slot * 2 + 1] = 0.0f;
+        }
+        return;
+    }
+    const int b0 = k0 + warp * KA_BK;                         // this warp's block
+    const bool mine = b0 <= k1 && (min(k1, b0 + KA_BK - 1) >= lo || b0 < keep);
+    bf16* k_s = kv_s + (size_t)warp * KA_BK * ld;
+    if (mine) {
+        const int* table = a.block_table + (size_t)a.row_req[r] * a.max_blocks;
+        keys_load_rows(a, table, kvh, b0, k1, k_s, 0, 1, 32);
+        keys_load_rows(a, table, kvh, b0, k1, k_s, 32, 1, 32);
+    }
+    cp_async_commit();
+    const int vec = a.D / 8;
+    for (int g = warp; g < 16; g += 4)
+        for (int c = lane; c < vec; c += 32) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (g < heads_here) v = *reinterpret_cast<const uint4*>(a.q + ((size_t)r * a.nq + head0 + g) * a.D + c * 8);
+            *reinterpret_cast<uint4*>(q_s + g * ld + c * 8) = v;
+        }
+
+    float o[2 * NV][4];
+#pragma unroll
+    for (int i = 0; i < 2 * NV; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[i][e] = 0.0f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    const int pos_r[2] = {pos, pos}, lo_r[2] = {lo, lo};
+    const int head_r[2] = {min(head0 + lane / 4, a.nq - 1), min(head0 + lane / 4 + 8, a.nq - 1)};
+    cp_async_wait<0>();
+    __syncthreads();                    // the query tile and every warp's own keys are in shared memory
+    if (mine) {
+        float s[KA_BK / 8][4];
+        keys_scores<KA_BK / 8>(s, q_s, k_s, 0, a.D, ld, lane);
+        float corr[2];                  // of nothing: this is the warp's only pass
+        keys_softmax_step<KA_BK / 8>(s, b0, pos_r, lo_r, head_r, k1, a, a.dist_bias, a.nq, m_run, l_run, corr, lane);
+#pragma unroll
+        for (int j = 0; j < KA_BK / 16; ++j) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(s[2 * j][0], s[2 * j][1]);
+            pa[1] = pack_bf16(s[2 * j][2], s[2 * j][3]);
+            pa[2] = pack_bf16(s[2 * j + 1][0], s[2 * j + 1][1]);
+            pa[3] = pack_bf16(s[2 * j + 1][2], s[2 * j + 1][3]);
+#pragma unroll
+            for (int d2 = 0; d2 < NV; ++d2) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, k_s + (j * 16 + (lane % 8) + ((lane / 8) % 2) * 8) * ld + vcol0 + d2 * 16 + (lane / 16) * 8);
+                mma_bf16(o[2 * d2], pa, b[0], b[1]);
+                mma_bf16(o[2 * d2 + 1], pa, b[2], b[3]);
+            }
+        }
+    }
+    __syncthreads();                    // the key blocks are no longer read
+    keys_decode_finish<NV>(a, kv_s, o, m_run, l_run, heads_here, head0, vcol0, ri, split, chunk);
+}
+
 template <int NV>
 __global__ void __launch_bounds__(KA_THREADS) keys_decode_kernel(KeysArgs a) {
     extern __shared__ __align__(16) uint8_t smem_bytes[];
@@ -370,42 +511,7 @@ __global__ void __launch_bounds__(KA_THREADS) keys_decode_kernel(KeysArgs a) {
         }
         __syncthreads();
     }
-    // every warp leaves its partial in shared memory (the key blocks are no longer read), then the block adds the four
-    float* o_w = reinterpret_cast<float*>(kv_s) + (size_t)warp * (16 * DVC + 32);     // [16][DVC] then [16][2]
-    float* ml_w = o_w + 16 * DVC;
-#pragma unroll
-    for (int i = 0; i < 2 * NV; ++i)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) o_w[(lane / 4 + 8 * (e >> 1)) * DVC + i * 8 + (lane % 4) * 2 + (e & 1)] = o[i][e];
-    if (lane % 4 == 0) {
-        ml_w[(lane / 4) * 2] = m_run[0];
-        ml_w[(lane / 4) * 2 + 1] = l_run[0];
-        ml_w[(lane / 4 + 8) * 2] = m_run[1];
-        ml_w[(lane / 4 + 8) * 2 + 1] = l_run[1];
-    }
-    __syncthreads();
-    const float* base = reinterpret_cast<const float*>(kv_s);
-    constexpr int WS = 16 * DVC + 32;
-    for (int idx = threadIdx.x; idx < heads_here * DVC; idx += KA_THREADS) {
-        const int g = idx / DVC, dd = idx % DVC;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, base[w * WS + 16 * DVC + g * 2]);
-        float acc = 0.0f, L = 0.0f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float mw = base[w * WS + 16 * DVC + g * 2];
-            const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - M);
-            acc += f * base[w * WS + g * DVC + dd];
-            L += f * base[w * WS + 16 * DVC + g * 2 + 1];
-        }
-        const size_t slot = ((size_t)ri * a.nq + head0 + g) * a.max_splits + split;
-        if (vcol0 + dd < a.dv) a.part_o[slot * a.dv + vcol0 + dd] = acc;
-        if (dd == 0 && chunk == 0) {
-            a.part_ml[slot * 2] = M;
-            a.part_ml[slot * 2 + 1] = L;
-        }
-    }
+    keys_decode_finish<NV>(a, kv_s, o, m_run, l_run, heads_here, head0, vcol0, ri, split, chunk);
 }
 
 // One block per (row, query head): the row's partials of splits 0 .. pos / 256, weighted by exp2(max_s - max), added
@@ -490,8 +596,20 @@ static int keys_launch_decode(const KeysArgs& a, int R, int splits, int n_chunks
     }
     const int G = a.nq / a.nkv;
     const dim3 grid(splits, a.nkv * ((G + 15) / 16) * n_chunks, R);
-    auto kern = keys_decode_kernel<NV>;
-    SHARPI_LAUNCH_PDL(kern, grid, KA_THREADS, smem, stream, a);
+    const size_t smem_warp = (size_t)(4 * KA_BK + 16) * a.ld * 2;
+    if (smem_warp <= 113 * 1024) {
+        static size_t configured_warp = 0;
+        if (smem_warp > configured_warp) {
+            if (cudaFuncSetAttribute(keys_decode_warp_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_warp) != cudaSuccess)
+                return SHARPI_LAUNCH_FAILED;
+            configured_warp = smem_warp;
+        }
+        auto kern = keys_decode_warp_kernel<NV>;
+        SHARPI_LAUNCH_PDL(kern, grid, KA_THREADS, smem_warp, stream, a);
+    } else {
+        auto kern = keys_decode_kernel<NV>;
+        SHARPI_LAUNCH_PDL(kern, grid, KA_THREADS, smem, stream, a);
+    }
     SHARPI_LAUNCH_PDL(keys_merge_kernel, dim3(R, a.nq), KA_THREADS, 0, stream, a);
     return SHARPI_OK;
 }

@@ -72,9 +72,12 @@ __global__ void __launch_bounds__(SSD_THREADS) ssd_scan_kernel(SsdArgs a) {
         const int n = 32 * (j / 4) + 4 * lane + (j % 4);
         S[j] = (live && n < N) ? st[(size_t)n * P + v] : 0.0f;
     }
-    // what cp.async never writes is zero: states behind N, value columns behind P
-    for (int i = threadIdx.x; i < SSD_STAGES * STAGE; i += SSD_THREADS) smem[i] = 0.0f;
-    __syncthreads();
+    // what cp.async never writes is zero: states behind N, value columns behind P (where there are any: a block that
+    // serves a single row would otherwise spend a third of its instructions here)
+    if (N < NP || (blockIdx.x + 1) * SSD_COLS > P) {
+        for (int i = threadIdx.x; i < SSD_STAGES * STAGE; i += SSD_THREADS) smem[i] = 0.0f;
+        __syncthreads();
+    }
     const bool vec = (N % 4 == 0) && (a.ld_x % 4 == 0) && ((a.col_b + g * N) % 4 == 0) && ((a.col_c + g * N) % 4 == 0) &&
                      ((reinterpret_cast<uintptr_t>(a.xbc) & 15) == 0);
     const int n_chunks = (rows + SSD_CH - 1) / SSD_CH;
