@@ -73,8 +73,8 @@ CASE_B = _top(61, 52, 1e-4, 1.0, 1.0, [
 # 128), a window of exactly a page with 3 kept positions and one of 130 with 64, a table of 32 rows; two groups
 # of 64 states; a single expert.
 CASE_C = _top(131, 128, 1e-6, 4.0, 0.5, [
-    _lat(4, 32, 32, 48, 64, 96, 0.35, (32, 50000.0), _moe(1, 1, 32, 32)),
-    _att(4, 1, 64, 0.4, 32, 120, 64, 3, _moe(8, 2, 32, 48)),
+    _lat(4, 32, 32, 48, 64, 96, 0.35, (32, 30000.0), _moe(1, 1, 32, 32)),
+    _att(4, 1, 64, 0.4, 32, 150, 64, 3, _moe(8, 2, 32, 48)),
     _ssd(4, 32, 64, 2, 4, 1, _moe(4, 1, 64, 0)),
     _att(2, 2, 64, 0.3, 16, 200, 130, 64, None),
     _lat(2, 64, 16, 32, 48, 64, 0.3, (16, 1000.0), None),

@@ -150,7 +150,7 @@ def test_a_window_with_kept_positions_holds_their_pages():
 
 
 # -- the distance table -------------------------------------------------------------------------
-@pytest.mark.parametrize("rows,far", [(2, 2), (2, 3), (4, 9), (8, 40), (32, 120), (16, 200), (12, 64), (10, 16), (6, 3)])
+@pytest.mark.parametrize("rows,far", [(2, 2), (2, 3), (4, 9), (8, 40), (32, 150), (16, 200), (12, 64), (10, 16), (6, 3)])
 def test_distance_table_rows_are_the_plain_buckets(rows, far):
     from sharpinference_b200.parts import distance_bias_table
     rel = torch.arange(rows * 3, dtype=torch.float32).view(rows, 3)
@@ -163,12 +163,12 @@ def test_distance_table_rows_are_the_plain_buckets(rows, far):
 
 
 def test_plain_buckets_are_exact_near_and_logarithmic_far():
-    rows, far = 32, 120
+    rows, far = 32, 150
     assert [plain.distance_bucket(n, rows, far) for n in range(16)] == list(range(16))
     got = [plain.distance_bucket(n, rows, far) for n in range(16, 400)]
     assert got == sorted(got) and got[0] == 16 and got[-1] == 31
     first_last = next(n for n in range(16, 400) if plain.distance_bucket(n, rows, far) == 31)
-    assert 16 * (120 / 16) ** (15 / 16) <= first_last <= 120
+    assert 16 * (150 / 16) ** (15 / 16) <= first_last <= 150
 
 
 # -- the plain implementation against itself ---------------------------------------------------
