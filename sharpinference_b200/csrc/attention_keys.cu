@@ -18,6 +18,8 @@
 //                         head (they are the 16 rows of the MMA, so a key is read once for all of them), one split of
 //                         256 keys at an absolute multiple of 256, one value chunk; its four warps take 16 keys each
 //                         of every block of 64.  It leaves an unnormalised partial (max, sum, weighted values);
+//   keys_decode_warp_kernel   the same CTA where shared memory holds a split's 256 keys twice an SM: a warp owns one
+//                         block of 64 keys, asks for it at once and takes it in one pass;
 //   keys_merge_kernel     adds a row's partials in the order of the splits.
 // Blocks and splits sit at absolute positions and are added in ascending order, so a row's result depends on its
 // position and keys alone, not on how a prompt was cut or on the rest of the batch.
