@@ -240,7 +240,7 @@ def _paged_keys(keys, page_size, seed):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("window,keep,page", [(72, 20, 64), (33, 5, 16), (64, 3, 64), (130, 64, 64), (5, 0, 16), (1, 2, 16),
+@pytest.mark.parametrize("window,keep,page", [(75, 21, 64), (33, 5, 16), (64, 3, 64), (130, 64, 64), (5, 0, 16), (1, 2, 16),
                                               (0, 0, 64)])
 def test_keys_as_values_attention_with_one_key_that_stands_out(window, keep, page, dtype):
     """For a query at the end of 300 positions, one key at a time is made to stand out (a score of 36 against at
@@ -355,6 +355,55 @@ def test_tensor_core_attention_over_keys_only_pages(nq, nkv, d, dv, page):
                           dtype=torch.int32, device=DEV)
     ops.attention_keys_prefill(q, kv, bt, tiles2, other, **kw)
     assert torch.equal(other[:233], out[:233])
+
+
+@pytest.mark.parametrize("d,dv,window,keep", [(80, 80, 100, 3), (320, 256, 300, 70), (128, 128, 256, 0), (16, 16, 7, 257)])
+def test_single_rows_with_whole_splits_behind_the_window(d, dv, window, keep):
+    """Single rows deep in a sequence of 1200 positions: between the kept first positions and the window lie whole
+    splits of 256 keys that the row does not see, and the window's lower edge falls inside a split and at its border.
+    Row sizes on both sides of the size at which a CTA holds all keys of a split (a block a warp) or a ring of two
+    blocks; one far kept key is made to carry a head's row."""
+    from sharpinference_b200.kernels import ops
+    T, nq, nkv, page, far, rows_rel = 1200, 6, 2, 64, 500, 12
+    g = torch.Generator().manual_seed(d + window)
+    rel = torch.randn(rows_rel, nq, generator=g)
+    table = torch.stack([rel[plain.distance_bucket(n, rows_rel, far)] for n in range(far + 1)])
+    keys = torch.randn(T, nkv, d, generator=g).to(torch.bfloat16)
+    q = torch.randn(T, nq, d, generator=g)
+    if keep:
+        q[:, 0] = 12.0 * keys[keep - 1, 0].float() / math.sqrt(d)         # head 0 asks for the last kept key
+    q = q.to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    vis = plain.window_with_first(T, window, keep)
+    dist = (torch.arange(T)[:, None] - torch.arange(T)[None, :]).clamp(min=0, max=far)
+    rows = sorted({T - 1, 1023, 1024, 1024 + window - 1, 1024 + window, 767 + window, 768 + window, 700, 255, 256, keep + window,
+                   max(keep + window - 1, 0)} & set(range(T)))
+    want = torch.empty(len(rows), nq, dv, dtype=F64)
+    for h in range(nq):
+        kh = keys[:, h // (nq // nkv)].double()
+        p = plain.softmax_rows(q[:, h].double() @ kh.T * scale + table.double()[dist, h], vis)
+        want[:, h] = (p @ kh[:, :dv])[rows]
+    if keep:
+        p0 = plain.softmax_rows(q[:, 0].double() @ keys[:, 0].double().T * scale + table.double()[dist, 0], vis)
+        assert float(p0[T - 1, keep - 1]) > 0.5 and not bool(vis[T - 1, keep])
+    kv, bt = _paged_keys(keys.float(), page, seed=d)
+    kv, bt = kv.to(torch.bfloat16).to(DEV), bt.to(DEV)
+    rr = torch.zeros(T, dtype=torch.int32, device=DEV)
+    pos = torch.arange(T, dtype=torch.int32, device=DEV)
+    some = torch.tensor(rows, dtype=torch.int32, device=DEV)
+    out = torch.zeros(T, nq * dv, dtype=torch.bfloat16, device=DEV)
+    kw = dict(nq=nq, nkv=nkv, d=d, dv=dv, page_size=page, mask_kind=ops.MASK_WINDOW, mask_span=window, scale=scale,
+              keep_first=keep, dist_bias=table.to(DEV))
+    ops.attention_keys_decode(q.to(DEV).view(T, nq * d), kv, bt, rr, pos, out, rows=some, num_rows=len(rows), max_context=T, **kw)
+    got = out.double().cpu().view(T, nq, dv)[rows]
+    assert float((got - want).abs().max()) < 4e-2
+    # the same rows as the tails of tiles give the same values
+    tiles = torch.tensor([[r - 10, 11, r - 10, 0] for r in rows if r >= 10], dtype=torch.int32, device=DEV)
+    tiled = torch.zeros_like(out)
+    ops.attention_keys_prefill(q.to(DEV).view(T, nq * d), kv, bt, tiles, tiled, **kw)
+    keep_rows = [k for k, r in enumerate(rows) if r >= 10]
+    got_t = tiled.double().cpu().view(T, nq, dv)[[rows[k] for k in keep_rows]]
+    assert float((got_t - want[keep_rows]).abs().max()) < 4e-2
 
 
 def test_distance_bias_is_not_scaled_and_reads_the_head_of_the_query():
