@@ -188,12 +188,14 @@ def test_state_space_duality_scan(heads, groups, N, P):
     assert float(state[4].min()) == 7.0 and float(state[1].abs().max()) == 0.0
 
 
-def test_scan_rows_do_not_depend_on_the_cut():
+@pytest.mark.parametrize("N,P", [(48, 24), (64, 32), (128, 64)])
+def test_scan_rows_do_not_depend_on_the_cut(N, P):
     """The walk adds a row's parts in one fixed order: a prompt in one step and the same prompt in portions of 1, 2
-    and 16 rows give the same bits, row by row and in the state left behind."""
+    and 16 rows give the same bits, row by row and in the state left behind (sizes that leave padding in the walk's
+    buffers and sizes that leave none; single rows and longer portions are launched differently)."""
     from sharpinference_b200.kernels import ops
     g = torch.Generator().manual_seed(3)
-    heads, groups, N, P, T = 3, 1, 48, 24, 67
+    heads, groups, T = 3, 1, 67
     inner, bc = heads * P, groups * N
     xbc, dt = f32(torch.randn(T, inner + 2 * bc, generator=g)), f32(torch.randn(T, heads, generator=g))
     vec = lambda: f32(torch.randn(heads, generator=g) - 1.0)
