@@ -42,6 +42,8 @@ struct DecodeArgs {
     int nq, nkv, max_blocks, page_size, page_shift, mask_kind, mask_span, max_splits;
     int num_rows;             // R
     float scale_log2;         // softmax scale * log2(e)
+    float cap_in, cap_out;    // score cap: cap_in = scale / softcap, cap_out = softcap * log2(e); cap_out = 0: none
+    const float* sinks;       // [nq] or null: exp(sink) of the head joins the denominator in the merge
     int* status;              // device word for a wait that gave up (TMA path)
 };
 
@@ -267,7 +269,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(const
                 for (int e = 0; e < 4; ++e) {
                     const int key = chunk0 + nt * 8 + (lane % 4) * 2 + (e & 1);
                     const bool valid = key >= k_begin && key <= k_end;
-                    s[nt][e] = valid ? s[nt][e] * a.scale_log2 : -INFINITY;
+                    const float sc = a.cap_out > 0.0f ? a.cap_out * tanhf(s[nt][e] * a.cap_in) : s[nt][e] * a.scale_log2;
+                    s[nt][e] = valid ? sc : -INFINITY;
                     m_c[e >> 1] = fmaxf(m_c[e >> 1], s[nt][e]);
                 }
             float corr[2], l_c[2] = {0.0f, 0.0f};
@@ -390,7 +393,9 @@ __global__ void __launch_bounds__(MERGE_THREADS) attn_decode_merge_kernel(Decode
     const float2* ml = reinterpret_cast<const float2*>(a.part_ml) + slot0;
     float m = -INFINITY;
     for (int s = threadIdx.x; s < n_s; s += blockDim.x) m = fmaxf(m, ml[s].x);
-    const float M = block_max(m, scratch);
+    // a sink is one more term of the denominator, exp2(sink - M), with M the larger of the sink and every split's maximum
+    const float sink = a.sinks ? a.sinks[head] * 1.4426950408889634f : -INFINITY;
+    const float M = fmaxf(block_max(m, scratch), sink);
     const bool active = lane < D / 4;
     const float4* po = reinterpret_cast<const float4*>(a.part_o + slot0 * D) + (active ? lane : 0);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -417,7 +422,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) attn_decode_merge_kernel(Decode
     __syncthreads();
     if (threadIdx.x < D / 4) {
         float4 o = acc_s[0][threadIdx.x];
-        float L = l_s[0];
+        float L = l_s[0] + (a.sinks ? exp2f(sink - M) : 0.0f);
         for (int w = 1; w < warps; ++w) {
             const float4 t = acc_s[w][threadIdx.x];
             o.x += t.x; o.y += t.y; o.z += t.z; o.w += t.w;
@@ -485,7 +490,8 @@ SHARPI_API int sharpi_attention_decode(const void* q, const void* kv, const int*
                                        const int* positions, const int* rows, float* part_o, float* part_ml,
                                        void* out, int* status, int num_pages, int R, int nq, int nkv, int d,
                                        int max_blocks, int page_size, int mask_kind, int mask_span, int splits,
-                                       int items, float scale, cudaStream_t stream) {
+                                       int items, float scale, float softcap, const float* sinks,
+                                       cudaStream_t stream) {
     if (R <= 0) return SHARPI_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || max_blocks <= 0 || splits <= 0 || R > 65535 ||
         nq > 65535)
@@ -497,6 +503,9 @@ SHARPI_API int sharpi_attention_decode(const void* q, const void* kv, const int*
     a.positions = positions; a.rows = rows; a.part_o = part_o; a.part_ml = part_ml; a.out = (bf16*)out;
     a.nq = nq; a.nkv = nkv; a.max_blocks = max_blocks; a.page_size = page_size; a.mask_kind = mask_kind;
     a.mask_span = mask_span; a.max_splits = splits; a.scale_log2 = scale * 1.4426950408889634f;
+    a.cap_in = softcap > 0.0f ? scale / softcap : 0.0f;
+    a.cap_out = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
+    a.sinks = sinks;
     a.num_rows = R;
     const long long all = (long long)R * splits;
     if (items <= 0 || items > all) items = (int)(all < 2147483647LL ? all : 2147483647LL);

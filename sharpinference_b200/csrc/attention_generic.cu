@@ -19,7 +19,8 @@
 // two readings of one cached latent.  `keep_first` > 0 (window mask): the first `keep_first` positions of a
 // sequence stay visible beyond the window; the walk then runs over the kept positions below the window first and
 // the window after them.  `dist_bias` [far + 1, nq]: a number added to the scaled score by the distance
-// pos - key (distances beyond `far` read row `far`).
+// pos - key (distances beyond `far` read row `far`).  `softcap` > 0 bends the scaled score to softcap * tanh(s /
+// softcap) (before any bias); `sinks` [nq] adds exp(sink) of the head to the softmax's denominator.
 #include "common.cuh"
 
 constexpr int ATT_THREADS = 128;
@@ -40,6 +41,8 @@ struct PagedAttnArgs {
     int keep_first;          // window mask: positions below this stay visible
     const float* dist_bias;  // [dist_far + 1, nq] or null
     int dist_far;
+    float softcap;           // > 0: the scaled score s becomes softcap * tanh(s / softcap)
+    const float* sinks;      // [nq] or null: exp(sinks[h]) joins the softmax's denominator, with no key and no value
 };
 
 template <typename TS>
@@ -86,6 +89,7 @@ __global__ void paged_attention_generic_kernel(PagedAttnArgs a) {
                 float dot = 0.0f;
                 for (int i = 0; i < d; ++i) dot += q_s[i] * to_float(krow[i]);
                 s = dot * a.scale;
+                if (a.softcap > 0.0f) s = a.softcap * tanhf(s / a.softcap);
                 if (a.dist_bias) s += a.dist_bias[(size_t)min(pos - key, a.dist_far) * a.nq + h];
             }
         }
@@ -115,7 +119,17 @@ __global__ void paged_attention_generic_kernel(PagedAttnArgs a) {
         }
     }
     TS* orow = (TS*)a.out + ((size_t)t * a.nq + h) * d;
-    const float inv_l = 1.0f / l_run;
+    float shrink = 1.0f;
+    if (a.sinks) {              // the sink counts once: exp(sink - m) in the denominator, against the larger of the two
+        const float sink = a.sinks[h];
+        if (sink > m_run) {
+            shrink = expf(m_run - sink);
+            l_run = l_run * shrink + 1.0f;
+        } else {
+            l_run += expf(sink - m_run);
+        }
+    }
+    const float inv_l = shrink / l_run;
 #pragma unroll
     for (int r = 0; r < DPT; ++r) {
         const int i = threadIdx.x + r * ATT_THREADS;
@@ -128,7 +142,7 @@ SHARPI_API int sharpi_paged_attention_generic(const void* q, const void* kv_base
                                               int T, int nq, int nkv, int d, int max_blocks, int page_size,
                                               int mask_kind, int mask_span, float scale, int kv_planes,
                                               int keep_first, const float* dist_bias, int dist_far,
-                                              cudaStream_t stream) {
+                                              float softcap, const float* sinks, cudaStream_t stream) {
     if (T <= 0) return SHARPI_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || d > ATT_MAX_D || nq > 65535 || page_size <= 0 ||
         max_blocks <= 0)
@@ -137,6 +151,7 @@ SHARPI_API int sharpi_paged_attention_generic(const void* q, const void* kv_base
     if ((kv_planes != 1 && kv_planes != 2) || keep_first < 0 || (dist_bias && dist_far < 0)) return SHARPI_BAD_ARGUMENT;
     PagedAttnArgs a;
     a.kv_planes = kv_planes; a.keep_first = keep_first; a.dist_bias = dist_bias; a.dist_far = dist_far;
+    a.softcap = softcap; a.sinks = sinks;
     a.q = q; a.kv_base = kv_base; a.block_table = block_table; a.row_req = row_req; a.positions = positions;
     a.out = out; a.T = T; a.nq = nq; a.nkv = nkv; a.d = d; a.max_blocks = max_blocks; a.page_size = page_size;
     a.mask_kind = mask_kind; a.mask_span = mask_span; a.scale = scale;

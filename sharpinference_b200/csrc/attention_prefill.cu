@@ -12,7 +12,8 @@
 // f16 mma.sync, contiguous per-sequence cache, causal + optional window;
 // src/SharpInference.Cuda/CudaTextKernels.cs:7657, :8086-8110).  Differences: the cache is paged,
 // the chunk mask exists, keys are bf16, and tiles come from a list so that portions of several
-// requests share one launch.
+// requests share one launch.  Two optional rules: a score cap, s -> softcap * tanh(s / softcap) on the scaled score,
+// and a sink per head whose exponential joins the softmax's denominator with no key and no value.
 #include "common.cuh"
 #include "mma_sync.cuh"
 
@@ -30,6 +31,8 @@ struct PrefillArgs {
     bf16* out;                // [T, nq * D]
     int nq, nkv, max_blocks, page_size, mask_kind, mask_span;
     float scale_log2;
+    float cap_in, cap_out;    // softcap > 0: cap_in = scale / softcap, cap_out = softcap * log2(e); else cap_out = 0
+    const float* sinks;       // [nq] or null
 };
 
 template <int D>
@@ -145,7 +148,8 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attn_prefill_kernel(PrefillArgs
                     const int key = key0 + nt * 8 + (lane % 4) * 2 + (e & 1);
                     const int h = e >> 1;
                     const bool valid = key <= pos_r[h] && key >= lo_r[h];
-                    s[nt][e] = valid ? s[nt][e] * a.scale_log2 : -INFINITY;
+                    const float sc = a.cap_out > 0.0f ? a.cap_out * tanhf(s[nt][e] * a.cap_in) : s[nt][e] * a.scale_log2;
+                    s[nt][e] = valid ? sc : -INFINITY;
                     m_c[h] = fmaxf(m_c[h], s[nt][e]);
                 }
             float corr[2], l_c[2] = {0.0f, 0.0f};
@@ -199,7 +203,17 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attn_prefill_kernel(PrefillArgs
     for (int h = 0; h < 2; ++h) {
         const int r = warp * 16 + lane / 4 + 8 * h;
         if (r < n_rows) {
-            const float inv = 1.0f / l_run[h];
+            float l = l_run[h], shrink = 1.0f;
+            if (a.sinks) {      // exp(sink - m) joins the denominator (in log2 units here), against the larger of the two
+                const float sink = a.sinks[head] * 1.4426950408889634f;
+                if (sink > m_run[h]) {
+                    shrink = exp2f(m_run[h] - sink);
+                    l = l * shrink + 1.0f;
+                } else {
+                    l += exp2f(sink - m_run[h]);
+                }
+            }
+            const float inv = shrink / l;
             bf16* dst = a.out + ((size_t)(row0 + r) * a.nq + head) * D + (lane % 4) * 2;
 #pragma unroll
             for (int i = 0; i < D / 8; ++i) {
@@ -227,7 +241,8 @@ static int launch_prefill(const PrefillArgs& a, int n_tiles, cudaStream_t stream
 
 SHARPI_API int sharpi_attention_prefill(const void* q, const void* kv, const int* block_table, const int* tiles,
                                         void* out, int n_tiles, int nq, int nkv, int d, int max_blocks, int page_size,
-                                        int mask_kind, int mask_span, float scale, cudaStream_t stream) {
+                                        int mask_kind, int mask_span, float scale, float softcap, const float* sinks,
+                                        cudaStream_t stream) {
     if (n_tiles <= 0) return SHARPI_OK;
     if (n_tiles > 65535) return SHARPI_BAD_ARGUMENT;        // tiles are the grid's second extent
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || max_blocks <= 0 || nq > 65535)
@@ -239,6 +254,9 @@ SHARPI_API int sharpi_attention_prefill(const void* q, const void* kv, const int
     a.q = (const bf16*)q; a.kv = (const bf16*)kv; a.block_table = block_table; a.tiles = tiles; a.out = (bf16*)out;
     a.nq = nq; a.nkv = nkv; a.max_blocks = max_blocks; a.page_size = page_size; a.mask_kind = mask_kind;
     a.mask_span = mask_span; a.scale_log2 = scale * 1.4426950408889634f;
+    a.cap_in = softcap > 0.0f ? scale / softcap : 0.0f;
+    a.cap_out = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
+    a.sinks = sinks;
     switch (d) {
         case 16: return launch_prefill<16>(a, n_tiles, stream);
         case 32: return launch_prefill<32>(a, n_tiles, stream);

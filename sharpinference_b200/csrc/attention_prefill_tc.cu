@@ -24,6 +24,8 @@
 // the softmax of one hides the waits of the other.  Key blocks sit at absolute multiples of 64
 // positions: a row's result depends on its own position and keys only.
 // Every wait is bounded; a wait that gives up records a code in *status and the kernel winds down.
+// Two optional rules: a score cap (the CAP kernels: softcap * tanh(s / softcap) on the scaled score, formed from the
+// raw score with one ex2 and one division), and a sink per head whose exponential joins the row's denominator.
 //
 // Sizes: head size 64 or 128, pages of a multiple of 64 positions, bf16.  Everything else takes the
 // warp-level kernel (attention_prefill.cu) or the generic one.  The reference's counterparts are the
@@ -49,7 +51,17 @@ struct PrefillTcArgs {
     int* status;
     int nq, nkv, max_blocks, page_size, page_shift, mask_kind, mask_span;
     float scale_log2;
+    float cap_in, cap_out;    // score cap: cap_in = 2 log2(e) scale / softcap, cap_out = softcap * log2(e) (CAP kernels)
+    const float* sinks;       // [nq] or null: exp(sink) of the head joins the row's denominator
 };
+
+// softcap * tanh(s * scale / softcap) in log2 units, as cap_out * (1 - 2 / (1 + 2^(s * cap_in))): one ex2 and one
+// division, absolute error of a few 1e-7 of the cap.  -inf (a hidden score) stays -inf.
+__device__ __forceinline__ float capped_log2(float s, float cap_in, float cap_out) {
+    if (s == -INFINITY) return -INFINITY;
+    const float e = ex2_approx(s * cap_in);
+    return cap_out * (1.0f - __fdividef(2.0f, 1.0f + e));
+}
 
 // Two fp32 operations in one instruction (sm_100 has packed f32x2 forms): the softmax warps are bound by the
 // instructions they issue, so the scale-and-subtract and the row sum take pairs of columns at a time.
@@ -92,7 +104,7 @@ struct AttCfg {
     static constexpr int TMEM_COLS = 256;                  // 128 + D <= 256
 };
 
-template <int D>
+template <int D, bool CAP>
 __global__ void __launch_bounds__(TC_ATT_THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
                        const PrefillTcArgs a) {
@@ -279,7 +291,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 m1 = fmax3(m1, __uint_as_float(sv[c + 2]), __uint_as_float(sv[c + 3]));
             }
             const float m_mine = fmax3(m0, m1, fmaxf(__uint_as_float(sv[HALF - 2]), __uint_as_float(sv[HALF - 1])));
-            const float m_blk = fmaxf(m_mine, m_other) * scale;      // the same number in both threads of the row
+            // the same number in both threads of the row (the cap is monotone: the largest raw score is the largest capped one)
+            const float m_blk = CAP ? capped_log2(fmaxf(m_mine, m_other), a.cap_in, a.cap_out) : fmaxf(m_mine, m_other) * scale;
             // raise the reference maximum only when this block's maximum is far above it; the rows of a warp
             // share the decision to touch O (and the row's two warps decide alike), each row uses its own factor
             const bool raise = m_blk > m_ref + RAISE;               // also true for the row's first visible block
@@ -315,7 +328,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 #pragma unroll
             for (int c = 0; c < HALF; c += 2) {
                 float x0, x1;
-                unpack2(fma2(pack2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, neg_m2), x0, x1);
+                if (CAP) {
+                    x0 = capped_log2(__uint_as_float(sv[c]), a.cap_in, a.cap_out) + neg_m;
+                    x1 = capped_log2(__uint_as_float(sv[c + 1]), a.cap_in, a.cap_out) + neg_m;
+                } else {
+                    unpack2(fma2(pack2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, neg_m2), x0, x1);
+                }
                 const float e0 = ex2_approx(x0), e1 = ex2_approx(x1);
                 l2 = add2(l2, pack2(e0, e1));
                 __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
@@ -341,10 +359,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         float* l_s = reinterpret_cast<float*>(p_s);
         l_s[half * TQ + r] = l_run;
         named_barrier_all(1, SOFTMAX_WARPS * 32, true);
-        const float l_row = l_s[r] + l_s[TQ + r];          // the same order in both threads
+        float l_row = l_s[r] + l_s[TQ + r];                // the same order in both threads
+        float shrink = 1.0f;
+        if (a.sinks && m_ref != -INFINITY) {               // the sink against the row's reference (log2 units), whichever is larger
+            const float sink = a.sinks[head] * 1.4426950408889634f;
+            if (sink > m_ref) {
+                shrink = exp2f(m_ref - sink);
+                l_row = l_row * shrink + 1.0f;
+            } else {
+                l_row += exp2f(sink - m_ref);
+            }
+        }
         if (ok) {
             tcgen05_fence_after();
-            const float inv = 1.0f / l_row;
+            const float inv = shrink / l_row;
             bf16* dst = a.out + ((size_t)(row0 + r) * a.nq + head) * D;
 #pragma unroll
             for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
@@ -375,17 +403,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     }
 }
 
-template <int D>
+template <int D, bool CAP>
 static int launch_tc(const CUtensorMap& qm, const CUtensorMap& kvm, const PrefillTcArgs& a, int n_tiles, cudaStream_t stream) {
     using Cfg = AttCfg<D>;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(attn_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) !=
+        if (cudaFuncSetAttribute(attn_prefill_tc_kernel<D, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) !=
             cudaSuccess)
             return SHARPI_LAUNCH_FAILED;
         configured = true;
     }
-    attn_prefill_tc_kernel<D><<<dim3(a.nq, n_tiles), TC_ATT_THREADS, Cfg::SMEM, stream>>>(qm, kvm, a);
+    attn_prefill_tc_kernel<D, CAP><<<dim3(a.nq, n_tiles), TC_ATT_THREADS, Cfg::SMEM, stream>>>(qm, kvm, a);
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
 }
@@ -394,7 +422,7 @@ static int launch_tc(const CUtensorMap& qm, const CUtensorMap& kvm, const Prefil
 SHARPI_API int sharpi_attention_prefill_tc(const void* q, const void* kv, const int* block_table, const int* tiles,
                                            void* out, int* status, int T, int num_pages, int n_tiles, int nq, int nkv,
                                            int d, int max_blocks, int page_size, int mask_kind, int mask_span,
-                                           float scale, cudaStream_t stream) {
+                                           float scale, float softcap, const float* sinks, cudaStream_t stream) {
     if (n_tiles <= 0) return SHARPI_OK;
     if (n_tiles > 65535) return SHARPI_BAD_ARGUMENT;        // tiles are the grid's second extent
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || max_blocks <= 0 || nq > 65535 || !status) return SHARPI_BAD_ARGUMENT;
@@ -414,6 +442,14 @@ SHARPI_API int sharpi_attention_prefill_tc(const void* q, const void* kv, const 
     a.mask_span = mask_span; a.scale_log2 = scale * 1.4426950408889634f;
     a.page_shift = 0;
     while ((1 << a.page_shift) < page_size) ++a.page_shift;
-    if (d == 64) return launch_tc<64>(qm, kvm, a, n_tiles, stream);
-    return launch_tc<128>(qm, kvm, a, n_tiles, stream);
+    a.sinks = sinks;
+    a.cap_in = a.cap_out = 0.0f;
+    if (softcap > 0.0f) {
+        a.cap_in = 2.0f * 1.4426950408889634f * scale / softcap;
+        a.cap_out = softcap * 1.4426950408889634f;
+        if (d == 64) return launch_tc<64, true>(qm, kvm, a, n_tiles, stream);
+        return launch_tc<128, true>(qm, kvm, a, n_tiles, stream);
+    }
+    if (d == 64) return launch_tc<64, false>(qm, kvm, a, n_tiles, stream);
+    return launch_tc<128, false>(qm, kvm, a, n_tiles, stream);
 }

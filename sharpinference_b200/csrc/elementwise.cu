@@ -523,23 +523,110 @@ SHARPI_API int sharpi_add_dyt(float* x, const float* delta, const float* w, cons
     return SHARPI_OK;
 }
 
-// out = o * sigmoid(g): a gate on the concatenated heads of a mixer, `o` in the activation dtype (the attention
-// kernels' output), `g` the float32 product of the gate's projection; the sigmoid and the product are float32.
-template <typename TO>
-__global__ void __launch_bounds__(256) sigmoid_gate_kernel(const TO* o, const float* g, TO* out, long long n) {
+// ---------------------------------------------------------------------------------------
+// Residual add fused with a layer norm that has a weight and a bias:
+//   x += delta (in place unless `rows` gathers);  out = (x - mean) / sqrt(var + eps) * w + b
+// with var the mean of the squared deviations from the mean (formed in a second pass over the row, not as
+// E[x^2] - mean^2, so nothing cancels).  One block a row whatever the batch; a thread adds its elements in ascending
+// order and the block's tree is fixed, so a row's numbers depend on the row alone.  The row stays in shared memory
+// between the passes when it fits.  Same interface as sharpi_add_rmsnorm (optional unrounded float32 copy).
+// ---------------------------------------------------------------------------------------
+template <typename TO, bool CACHED>
+__global__ void __launch_bounds__(NORM_THREADS)
+add_layernorm_kernel(float* x, const float* __restrict__ delta, const float* __restrict__ w,
+                     const float* __restrict__ b, float eps, const int* __restrict__ rows, int H,
+                     TO* __restrict__ out, float* __restrict__ out32) {
+    __shared__ float scratch[32];
+    extern __shared__ float row_s[];
     pdl_wait();
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) out[i] = from_float<TO>(to_float(o[i]) / (1.0f + expf(-g[i])));
+    const int t = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[t] : t) * H;
+    float* xr = x + src;
+    const float* dr = delta ? delta + src : nullptr;
+    const bool write_back = dr && !rows;
+    float sum = 0.0f;
+    for (int i0 = threadIdx.x; i0 < H; i0 += NORM_UNROLL * NORM_THREADS) {
+        float v[NORM_UNROLL], d[NORM_UNROLL];
+#pragma unroll
+        for (int k = 0; k < NORM_UNROLL; ++k) {
+            const int i = i0 + k * NORM_THREADS;
+            v[k] = (i < H) ? xr[i] : 0.0f;
+            d[k] = (dr && i < H) ? dr[i] : 0.0f;
+        }
+#pragma unroll
+        for (int k = 0; k < NORM_UNROLL; ++k) {
+            const int i = i0 + k * NORM_THREADS;
+            if (i < H) {
+                if (dr) v[k] += d[k];
+                if (write_back) xr[i] = v[k];
+                if (CACHED) row_s[i] = v[k];
+                sum += v[k];
+            }
+        }
+    }
+    const float mean = block_sum(sum, scratch) / (float)H;
+    // without the cache the row is read again: x already holds the sum unless the rows were gathered
+    float sq = 0.0f;
+    for (int i = threadIdx.x; i < H; i += NORM_THREADS) {
+        const float v = CACHED ? row_s[i] : (xr[i] + ((dr && rows) ? dr[i] : 0.0f));
+        sq += (v - mean) * (v - mean);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)H + eps);
+    TO* orow = out + (size_t)t * H;
+    float* o32 = out32 ? out32 + (size_t)t * H : nullptr;
+    for (int i = threadIdx.x; i < H; i += NORM_THREADS) {
+        const float v = CACHED ? row_s[i] : (xr[i] + ((dr && rows) ? dr[i] : 0.0f));
+        const float y = (v - mean) * inv * w[i] + (b ? b[i] : 0.0f);
+        orow[i] = from_float<TO>(y);
+        if (o32) o32[i] = y;
+    }
 }
 
-SHARPI_API int sharpi_sigmoid_gate(const void* o, const float* g, void* out, int dtype, long long n,
+template <typename TO>
+static int launch_layernorm(float* x, const float* delta, const float* w, const float* b, float eps, const int* rows,
+                            int T, int H, TO* out, float* out32, cudaStream_t stream) {
+    if (H <= NORM_CACHE_FLOATS) {
+        auto kern = add_layernorm_kernel<TO, true>;
+        SHARPI_LAUNCH_PDL(kern, T, NORM_THREADS, (size_t)H * sizeof(float), stream, x, delta, w, b, eps, rows, H, out, out32);
+    } else {
+        auto kern = add_layernorm_kernel<TO, false>;
+        SHARPI_LAUNCH_PDL(kern, T, NORM_THREADS, 0, stream, x, delta, w, b, eps, rows, H, out, out32);
+    }
+    return SHARPI_OK;
+}
+
+SHARPI_API int sharpi_add_layernorm(float* x, const float* delta, const float* w, const float* b, float eps,
+                                    const int* rows, int T, int H, void* out, int out_dtype, float* out32,
+                                    cudaStream_t stream) {
+    if (T <= 0) return SHARPI_OK;
+    if (H <= 0 || !w) return SHARPI_BAD_ARGUMENT;
+    if (out_dtype == SHARPI_F32) return launch_layernorm<float>(x, delta, w, b, eps, rows, T, H, (float*)out, out32, stream);
+    if (out_dtype == SHARPI_BF16) return launch_layernorm<bf16>(x, delta, w, b, eps, rows, T, H, (bf16*)out, out32, stream);
+    return SHARPI_BAD_ARGUMENT;
+}
+
+// out = o * sigmoid(g): a gate on the concatenated heads of a mixer, `o` in the activation dtype (the attention
+// kernels' output), `g` the float32 product of the gate's projection ([rows, cols], rows `g_ld` floats apart); the
+// sigmoid and the product are float32.
+template <typename TO>
+__global__ void __launch_bounds__(256) sigmoid_gate_kernel(const TO* o, const float* g, TO* out, long long n, int cols,
+                                                           int g_ld) {
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long long gi = (g_ld == cols) ? i : (i / cols) * g_ld + i % cols;     // g may be a column range of a wider product
+    out[i] = from_float<TO>(to_float(o[i]) / (1.0f + expf(-g[gi])));
+}
+
+SHARPI_API int sharpi_sigmoid_gate(const void* o, const float* g, void* out, int dtype, long long n, int cols, int g_ld,
                                    cudaStream_t stream) {
     if (n <= 0) return SHARPI_OK;
+    if (cols <= 0 || g_ld < cols) return SHARPI_BAD_ARGUMENT;
     const unsigned blocks = (unsigned)((n + 255) / 256);
     if (dtype == SHARPI_F32)
-        SHARPI_LAUNCH_PDL(sigmoid_gate_kernel<float>, blocks, 256, 0, stream, (const float*)o, g, (float*)out, n);
+        SHARPI_LAUNCH_PDL(sigmoid_gate_kernel<float>, blocks, 256, 0, stream, (const float*)o, g, (float*)out, n, cols, g_ld);
     else if (dtype == SHARPI_BF16)
-        SHARPI_LAUNCH_PDL(sigmoid_gate_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)o, g, (bf16*)out, n);
+        SHARPI_LAUNCH_PDL(sigmoid_gate_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)o, g, (bf16*)out, n, cols, g_ld);
     else
         return SHARPI_BAD_ARGUMENT;
     return SHARPI_OK;

@@ -3,7 +3,10 @@
 //   router_topk   z = h Wr^T (float32), s = sigmoid(z); the k experts with the largest s + correction (the lowest
 //                 index among equals) are chosen; each weight is scale * s (without the correction), divided by the
 //                 sum of the chosen s first when `renormalize`.  A row's logits are one fixed sequence of additions
-//                 whatever else the step holds.
+//                 whatever else the step holds.  `bias` [E] (optional) is added to the logits.  `scoring` = 1
+//                 (softmax over the chosen): the k experts with the largest logits z are chosen and their weights are
+//                 scale * exp(z_i - max) / sum over the chosen of exp(z_j - max): the other experts' logits do not
+//                 enter.
 //   pair_tokens   after the (row, choice) pairs have been sorted by expert: the row each sorted pair belongs to.
 //   combine       out[t] = add[t] + sum over the row's k pairs of y[pair], in the order of the choices.
 //
@@ -22,7 +25,8 @@ template <int TOPK_ROWS>
 __global__ void __launch_bounds__(TOPK_WARPS * 32)
 router_topk_kernel(const float* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ correction,
                    int T, int H, int E, int k, float scale, int renormalize, int* __restrict__ expert_id,
-                   float* __restrict__ weight, float* __restrict__ scores_out, int stage_rows) {
+                   float* __restrict__ weight, float* __restrict__ scores_out, int stage_rows,
+                   const float* __restrict__ bias, int scoring) {
     extern __shared__ float smem[];                       // per row s [E], choice [E]; then the rows [ROWS][H] if they fit
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t0 = blockIdx.x * TOPK_ROWS;
@@ -64,9 +68,9 @@ router_topk_kernel(const float* __restrict__ h, const float* __restrict__ wr, co
         }
 #pragma unroll
         for (int r = 0; r < TOPK_ROWS; ++r) {
-            const float z = warp_sum((acc[r][0] + acc[r][1]) + (acc[r][2] + acc[r][3]));
+            const float z = warp_sum((acc[r][0] + acc[r][1]) + (acc[r][2] + acc[r][3])) + (bias ? bias[e] : 0.0f);
             if (lane == 0 && r < rows) {
-                const float s = 1.0f / (1.0f + expf(-z));
+                const float s = scoring == 1 ? z : 1.0f / (1.0f + expf(-z));
                 smem[(size_t)r * 2 * E + e] = s;
                 smem[(size_t)r * 2 * E + E + e] = correction ? s + correction[e] : s;
                 if (scores_out) scores_out[(size_t)(t0 + r) * E + e] = s;
@@ -78,7 +82,7 @@ router_topk_kernel(const float* __restrict__ h, const float* __restrict__ wr, co
     const int t = t0 + warp;
     float* s_s = smem + (size_t)warp * 2 * E;
     float* c_s = s_s + E;
-    float total = 0.0f;
+    float total = 0.0f, top = 0.0f;
     int mine = 0;                                          // lane j keeps the j-th choice
     for (int j = 0; j < k; ++j) {
         float best = -INFINITY;
@@ -99,8 +103,17 @@ router_topk_kernel(const float* __restrict__ h, const float* __restrict__ wr, co
             c_s[at] = -INFINITY;
         }
         if (lane == j) mine = at;
-        total += s_s[at];
+        if (scoring == 1) {                                // the first choice has the largest logit
+            if (j == 0) top = s_s[at];
+            total += expf(s_s[at] - top);
+        } else {
+            total += s_s[at];
+        }
         __syncwarp();
+    }
+    if (scoring == 1) {
+        if (lane < k) weight[(size_t)t * k + lane] = expf(s_s[mine] - top) * (scale / total);
+        return;
     }
     const float factor = renormalize ? scale / total : scale;
     if (lane < k) weight[(size_t)t * k + lane] = s_s[mine] * factor;      // k <= 32 is checked by the host
@@ -108,9 +121,9 @@ router_topk_kernel(const float* __restrict__ h, const float* __restrict__ wr, co
 
 SHARPI_API int sharpi_router_topk(const float* h, const float* wr, const float* correction, int T, int H, int E, int k,
                                   float scale, int renormalize, int* expert_id, float* weight, float* scores_out,
-                                  cudaStream_t stream) {
+                                  const float* bias, int scoring, cudaStream_t stream) {
     if (T <= 0) return SHARPI_OK;
-    if (H <= 0 || E <= 0 || k <= 0 || k > E || k > 32) return SHARPI_BAD_ARGUMENT;
+    if (H <= 0 || E <= 0 || k <= 0 || k > E || k > 32 || (scoring != 0 && scoring != 1)) return SHARPI_BAD_ARGUMENT;
     const int per_cta = T > TOPK_MANY_ROWS ? 4 : 1;
     size_t smem = (size_t)per_cta * 2 * E * sizeof(float);
     if (smem > 48 * 1024) return SHARPI_BAD_ARGUMENT;
@@ -118,10 +131,10 @@ SHARPI_API int sharpi_router_topk(const float* h, const float* wr, const float* 
     if (stage_rows) smem += (size_t)per_cta * H * sizeof(float);
     if (per_cta == 4)
         router_topk_kernel<4><<<(T + 3) / 4, TOPK_WARPS * 32, smem, stream>>>(
-            h, wr, correction, T, H, E, k, scale, renormalize, expert_id, weight, scores_out, stage_rows);
+            h, wr, correction, T, H, E, k, scale, renormalize, expert_id, weight, scores_out, stage_rows, bias, scoring);
     else
         router_topk_kernel<1><<<T, TOPK_WARPS * 32, smem, stream>>>(
-            h, wr, correction, T, H, E, k, scale, renormalize, expert_id, weight, scores_out, stage_rows);
+            h, wr, correction, T, H, E, k, scale, renormalize, expert_id, weight, scores_out, stage_rows, bias, scoring);
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
 }

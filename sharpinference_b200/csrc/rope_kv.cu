@@ -446,3 +446,77 @@ SHARPI_API int sharpi_rotate_heads(const void* in, int in_dtype, const int* posi
 #undef ROT_CASE
     return SHARPI_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// The same pass for layers whose q/k norm runs over the WHOLE projection: q (all heads side by side) is divided by
+// its root mean square and multiplied by a weight of that size, and so is k; no rotation.  Then the temperature
+// factor on q, the store of q and the scatter of k and v into the pages.
+//
+//   qkv      float32 [T, ld]: q (nq * d) | k (nkv * d) | v (nkv * d); a layer that reads another layer's cache
+//            brings q alone (`has_kv` = 0) and writes nothing.
+//   wq, wk   float32 [nq * d], [nkv * d]; q_count / k_count: what the mean of squares divides by (fewer than the
+//            row's elements when heads are padded with zeros).
+//
+// One block a row: the two sums of squares are formed by NORM_W_THREADS threads in a fixed order, so a row's
+// numbers do not depend on the batch.  float32 throughout; q and the pages take the activation dtype.
+// ---------------------------------------------------------------------------------------
+constexpr int NORM_W_THREADS = 256;
+
+template <typename TO>
+__global__ void __launch_bounds__(NORM_W_THREADS)
+qkv_post_wide_kernel(const float* qkv, int ld, const int* positions, const int* row_req, const int* block_table,
+                     const float* __restrict__ wq, const float* __restrict__ wk, float eps, int q_count, int k_count,
+                     TO* q_out, TO* kv_base, int nq, int nkv, int d, int max_blocks, int page_size, float temp_coef,
+                     float temp_every, int write_kv, int has_kv) {
+    __shared__ float scratch[32];
+    pdl_wait();
+    const int t = blockIdx.x;
+    const float* row = qkv + (size_t)t * ld;
+    const int nQ = nq * d, nK = nkv * d;
+    const int pos = positions[t];
+    const bool store_kv = has_kv && write_kv;
+    float sq = 0.0f, sk = 0.0f;
+    for (int i = threadIdx.x; i < nQ; i += NORM_W_THREADS) sq += row[i] * row[i];
+    if (store_kv)
+        for (int i = threadIdx.x; i < nK; i += NORM_W_THREADS) sk += row[nQ + i] * row[nQ + i];
+    sq = block_sum(sq, scratch);
+    float fq = 1.0f / sqrtf(sq / (float)q_count + eps);
+    if (temp_every > 0.0f) fq *= 1.0f + temp_coef * log1pf(floorf(((float)pos + 1.0f) / temp_every));
+    TO* qo = q_out + (size_t)t * nQ;
+    for (int i = threadIdx.x; i < nQ; i += NORM_W_THREADS) qo[i] = from_float<TO>(row[i] * fq * wq[i]);
+    if (!store_kv) return;
+    sk = block_sum(sk, scratch);
+    const float fk = 1.0f / sqrtf(sk / (float)k_count + eps);
+    const int page = block_table[(size_t)row_req[t] * max_blocks + pos / page_size];
+    if (page < 0) return;   // the host checks before the launch that every written position has a page
+    const size_t plane = (size_t)nkv * page_size * d;
+    TO* kdst = kv_base + (size_t)page * 2 * plane + (size_t)(pos % page_size) * d;
+    for (int i = threadIdx.x; i < nK; i += NORM_W_THREADS) {
+        const int head = i / d, e = i - head * d;
+        const size_t at = (size_t)head * page_size * d + e;
+        kdst[at] = from_float<TO>(row[nQ + i] * fk * wk[i]);
+        kdst[plane + at] = from_float<TO>(row[nQ + nK + i]);
+    }
+}
+
+SHARPI_API int sharpi_qkv_post_wide(const float* qkv, int ld, const int* positions, const int* row_req,
+                                    const int* block_table, const float* wq, const float* wk, float eps, int q_count,
+                                    int k_count, void* q_out, void* kv_base, int out_dtype, int T, int nq, int nkv,
+                                    int d, int max_blocks, int page_size, float temp_coef, float temp_every,
+                                    int write_kv, int has_kv, cudaStream_t stream) {
+    if (T <= 0) return SHARPI_OK;
+    if (nq <= 0 || nkv <= 0 || d <= 0 || page_size <= 0 || max_blocks <= 0 || !wq || q_count <= 0) return SHARPI_BAD_ARGUMENT;
+    if (has_kv && (!wk || k_count <= 0 || ld < (nq + 2 * nkv) * d)) return SHARPI_BAD_ARGUMENT;
+    if (ld < nq * d) return SHARPI_BAD_ARGUMENT;
+    if (out_dtype == SHARPI_F32)
+        SHARPI_LAUNCH_PDL(qkv_post_wide_kernel<float>, T, NORM_W_THREADS, 0, stream, qkv, ld, positions, row_req,
+                          block_table, wq, wk, eps, q_count, k_count, (float*)q_out, (float*)kv_base, nq, nkv, d,
+                          max_blocks, page_size, temp_coef, temp_every, write_kv, has_kv);
+    else if (out_dtype == SHARPI_BF16)
+        SHARPI_LAUNCH_PDL(qkv_post_wide_kernel<bf16>, T, NORM_W_THREADS, 0, stream, qkv, ld, positions, row_req,
+                          block_table, wq, wk, eps, q_count, k_count, (bf16*)q_out, (bf16*)kv_base, nq, nkv, d,
+                          max_blocks, page_size, temp_coef, temp_every, write_kv, has_kv);
+    else
+        return SHARPI_BAD_ARGUMENT;
+    return SHARPI_OK;
+}

@@ -34,12 +34,12 @@ SIGNATURES: Dict[str, Tuple[str, list]] = {
     "sharpi_add": ("elementwise", [P, P, P, LL, P]),
     "sharpi_timestamp": ("elementwise", [P, I, P]),
     "sharpi_qkv_post": ("rope_kv", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, I, I, I, P]),
-    "sharpi_paged_attention_generic": ("attention_generic", [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P, I, P]),
-    "sharpi_attention_decode": ("attention_decode", [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P]),
+    "sharpi_paged_attention_generic": ("attention_generic", [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P, I, F, P, P]),
+    "sharpi_attention_decode": ("attention_decode", [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, F, P, P]),
     "sharpi_attention_keys_prefill": ("attention_keys", [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, I, F, P]),
     "sharpi_attention_keys_decode": ("attention_keys", [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, I, I, F, P]),
-    "sharpi_attention_prefill": ("attention_prefill", [P, P, P, P, P, I, I, I, I, I, I, I, I, F, P]),
-    "sharpi_attention_prefill_tc": ("attention_prefill_tc", [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P]),
+    "sharpi_attention_prefill": ("attention_prefill", [P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, P, P]),
+    "sharpi_attention_prefill_tc": ("attention_prefill_tc", [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, F, P, P]),
     "sharpi_gemm_nt": ("gemm_generic", [P, I, P, I, P, P, P, P, I, I, I, I, I, P, P, P, P]),
     "sharpi_add_bias": ("elementwise", [P, P, I, I, P]),
     "sharpi_router_top1": ("moe", [P, P, I, I, I, I, P, P, P, P, P, P, P]),
@@ -56,7 +56,7 @@ SIGNATURES: Dict[str, Tuple[str, list]] = {
     "sharpi_sample_rows_no_alloc": ("sampling", [P, I, I, P, P, P, P, P, P, P]),
     "sharpi_bias_act": ("elementwise", [P, P, P, I, I, I, I, P]),
     "sharpi_concat2": ("elementwise", [P, P, P, P, I, I, I, P]),
-    "sharpi_router_topk": ("moe_topk", [P, P, P, I, I, I, I, F, I, P, P, P, P]),
+    "sharpi_router_topk": ("moe_topk", [P, P, P, I, I, I, I, F, I, P, P, P, P, I, P]),
     "sharpi_moe_pair_tokens": ("moe_topk", [P, I, I, P, P]),
     "sharpi_moe_combine": ("moe_topk", [P, P, P, I, I, I, P]),
     "sharpi_mlstm_recurrence": ("mlstm", [P, I, I, I, I, I, I, P, P, P, P, P, LL, I, I, I, I, I, I, F, F, P, P, P, P]),
@@ -75,13 +75,15 @@ SIGNATURES: Dict[str, Tuple[str, list]] = {
     "sharpi_gated_act": ("elementwise", [P, P, I, I, I, I, P]),
     "sharpi_tanh": ("elementwise", [P, P, I, LL, P]),
     "sharpi_scale": ("elementwise", [P, F, LL, P]),
-    "sharpi_sigmoid_gate": ("elementwise", [P, P, P, I, LL, P]),
+    "sharpi_sigmoid_gate": ("elementwise", [P, P, P, I, LL, I, I, P]),
     "sharpi_add_dyt": ("elementwise", [P, P, P, P, P, P, I, I, P, I, P, P]),
-    "sharpi_latent_down_post": ("latent", [P, I, I, I, I, I, P, P, F, P, P, P, I, I, P, P, P, I, I, I, I, I, P]),
-    "sharpi_head_major": ("latent", [P, I, I, I, I, I, I, P, I, P]),
-    "sharpi_head_minor": ("latent", [P, I, I, I, I, I, P, I, P]),
-    "sharpi_latent_q_join": ("latent", [P, P, P, P, I, I, I, I, I, I, I, P, I, P]),
+    "sharpi_latent_down_post": ("latent", [P, I, I, I, I, I, P, P, F, P, P, P, I, I, P, P, P, I, I, I, I, I, F, P]),
+    "sharpi_head_major": ("latent", [P, I, I, I, I, I, I, P, I, I, P]),
+    "sharpi_head_minor": ("latent", [P, I, I, I, I, I, P, I, P, I, P]),
+    "sharpi_latent_q_join": ("latent", [P, P, P, P, I, I, I, I, I, I, I, P, I, I, F, P]),
     "sharpi_ssd_scan": ("mamba2", [P, I, I, I, I, P, I, I, P, P, P, P, P, P, LL, P, I, I, I, I, I, I, P]),
+    "sharpi_add_layernorm": ("elementwise", [P, P, P, P, F, P, I, I, P, I, P, P]),
+    "sharpi_qkv_post_wide": ("rope_kv", [P, I, P, P, P, P, P, F, I, I, P, P, I, I, I, I, I, I, I, F, F, I, I, P]),
     "sharpi_gated_group_norm": ("mamba2", [P, P, I, P, F, I, I, I, P, I, P]),
 }
 

@@ -43,6 +43,18 @@ def _need(t: torch.Tensor, name: str, dtype=None) -> None:
         raise KernelError(f"{name} must have dtype {dtype}, found {t.dtype}")
 
 
+def _need_columns(t: torch.Tensor, name: str, dtype=None) -> int:
+    """A 2-D tensor whose rows are contiguous but may lie apart (a column range of a wider product); the distance
+    between two rows in elements."""
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (the engine has no CPU path); found device {t.device}")
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise KernelError(f"{name} must be 2-D with contiguous rows")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must have dtype {dtype}, found {t.dtype}")
+    return int(t.stride(0)) if t.shape[0] > 1 else int(t.shape[1])
+
+
 # ---------------------------------------------------------------------------------------
 def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out[t] = table[ids[t]]`` as fp32.  ``ids`` int32 [T], ``table`` [V, H] fp32 or bf16."""
@@ -207,13 +219,17 @@ def paged_attention_generic(q: torch.Tensor, kv_layer: torch.Tensor, block_table
                             row_req: torch.Tensor, positions: torch.Tensor, *, nq: int, nkv: int, d: int,
                             page_size: int, mask_kind: int, mask_span: int, scale: float,
                             out: Optional[torch.Tensor] = None, keep_first: int = 0,
-                            dist_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+                            dist_bias: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                            sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of every row over the keys it may see in its request's pages; [T, nq d].  A ``kv_layer`` with one
     plane (``[pages, 1, nkv, page_size, d]``) holds keys only and the values are the keys.  ``keep_first``: under
     a window mask the first positions of a sequence stay visible.  ``dist_bias`` float32 ``[far + 1, nq]`` is added
-    to the scaled score by the distance between query and key (distances beyond ``far`` read the last row)."""
+    to the scaled score by the distance between query and key (distances beyond ``far`` read the last row).
+    ``softcap`` > 0: the scaled score ``s`` becomes ``softcap * tanh(s / softcap)``.  ``sinks`` float32 ``[nq]``:
+    ``exp(sinks[h])`` joins the softmax's denominator of head ``h`` (no key, no value)."""
     _need(q, "q")
     _need(kv_layer, "kv_layer", q.dtype)
+    _check_sinks(sinks, nq)
     _need(block_table, "block_table", torch.int32)
     _need(row_req, "row_req", torch.int32)
     _need(positions, "positions", torch.int32)
@@ -229,9 +245,17 @@ def paged_attention_generic(q: torch.Tensor, kv_layer: torch.Tensor, block_table
                                                    dtype_code(q.dtype), T, nq, nkv, d, block_table.shape[-1],
                                                    page_size, mask_kind, mask_span, float(scale),
                                                    int(kv_layer.shape[1]), int(keep_first), _ptr(dist_bias),
-                                                   0 if dist_bias is None else dist_bias.shape[0] - 1, _stream()),
+                                                   0 if dist_bias is None else dist_bias.shape[0] - 1,
+                                                   float(softcap), _ptr(sinks), _stream()),
           "sharpi_paged_attention_generic")
     return out
+
+
+def _check_sinks(sinks: Optional[torch.Tensor], nq: int) -> None:
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32)
+        if sinks.numel() != nq:
+            raise KernelError(f"sinks has {sinks.numel()} entries for {nq} heads")
 
 
 FAST_ATTENTION_HEAD_SIZES = (16, 32, 48, 64, 80, 96, 112, 128)
@@ -264,7 +288,8 @@ def decode_splits(max_context: int, mask_kind: int, mask_span: int) -> int:
 def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, row_req: torch.Tensor,
                      positions: torch.Tensor, out: torch.Tensor, *, rows: Optional[torch.Tensor], num_rows: int,
                      nq: int, nkv: int, d: int, page_size: int, mask_kind: int, mask_span: int, scale: float,
-                     max_context: int, max_keys: Optional[int] = None) -> None:
+                     max_context: int, max_keys: Optional[int] = None, softcap: float = 0.0,
+                     sinks: Optional[torch.Tensor] = None) -> None:
     """Split-KV paged attention for rows that bring one query each (bfloat16).  ``rows`` (int32) names
     the rows to serve, or None for rows ``0 .. num_rows - 1``; results go to ``out[row]``.  ``max_context`` bounds
     the longest row (position + 1), ``max_keys`` the sum of position + 1 over the served rows: with it the launch
@@ -273,6 +298,7 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
     _need(kv_layer, "kv_layer", torch.bfloat16)
     _need(out, "out", torch.bfloat16)
     _need(block_table, "block_table", torch.int32)
+    _check_sinks(sinks, nq)
     if d not in FAST_ATTENTION_HEAD_SIZES:
         raise KernelError(f"head size {d} is not served by the tensor-core attention kernels "
                           f"({FAST_ATTENTION_HEAD_SIZES}); use the generic kernel")
@@ -286,7 +312,8 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
                                             part_ml.data_ptr(), out.data_ptr(), status_word(q.device).data_ptr(),
                                             kv_layer.shape[0], num_rows, nq, nkv, d,
                                             block_table.shape[-1], page_size, mask_kind, mask_span, splits, items,
-                                            float(scale), _stream()), "sharpi_attention_decode")
+                                            float(scale), float(softcap), _ptr(sinks), _stream()),
+          "sharpi_attention_decode")
 
 
 KEYS_ATTENTION_TILE = 64
@@ -352,20 +379,22 @@ def attention_keys_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: 
 
 def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor,
                       out: torch.Tensor, *, nq: int, nkv: int, d: int, page_size: int, mask_kind: int,
-                      mask_span: int, scale: float) -> None:
+                      mask_span: int, scale: float, softcap: float = 0.0,
+                      sinks: Optional[torch.Tensor] = None) -> None:
     """Paged attention for tiles of up to 64 consecutive rows of one request (bfloat16).  ``tiles`` is
     int32 [n, 4]: first row, number of rows, position of the first row, request index."""
     _need(q, "q", torch.bfloat16)
     _need(kv_layer, "kv_layer", torch.bfloat16)
     _need(out, "out", torch.bfloat16)
     _need(tiles, "tiles", torch.int32)
+    _check_sinks(sinks, nq)
     if d not in FAST_ATTENTION_HEAD_SIZES:
         raise KernelError(f"head size {d} is not served by the tensor-core attention kernels "
                           f"({FAST_ATTENTION_HEAD_SIZES}); use the generic kernel")
     check(kernel("sharpi_attention_prefill")(q.data_ptr(), kv_layer.data_ptr(), block_table.data_ptr(),
                                              tiles.data_ptr(), out.data_ptr(), tiles.shape[0], nq, nkv, d,
                                              block_table.shape[-1], page_size, mask_kind, mask_span, float(scale),
-                                             _stream()), "sharpi_attention_prefill")
+                                             float(softcap), _ptr(sinks), _stream()), "sharpi_attention_prefill")
 
 
 TC_PREFILL_TILE = 128
@@ -379,12 +408,14 @@ def tc_prefill_supported(dtype: torch.dtype, d: int, page_size: int) -> bool:
 
 def attention_prefill_tc(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor,
                          out: torch.Tensor, *, nq: int, nkv: int, d: int, page_size: int, mask_kind: int,
-                         mask_span: int, scale: float) -> None:
+                         mask_span: int, scale: float, softcap: float = 0.0,
+                         sinks: Optional[torch.Tensor] = None) -> None:
     """Paged attention for tiles of up to 128 consecutive rows of one request on tcgen05 / TMEM / TMA."""
     _need(q, "q", torch.bfloat16)
     _need(kv_layer, "kv_layer", torch.bfloat16)
     _need(out, "out", torch.bfloat16)
     _need(tiles, "tiles", torch.int32)
+    _check_sinks(sinks, nq)
     if not tc_prefill_supported(q.dtype, d, page_size):
         raise KernelError(f"the tcgen05 attention kernel takes head sizes 64 and 128 and pages of 64 * 2^k positions, "
                           f"found head size {d}, page size {page_size}")
@@ -392,7 +423,7 @@ def attention_prefill_tc(q: torch.Tensor, kv_layer: torch.Tensor, block_table: t
                                                 tiles.data_ptr(), out.data_ptr(), status_word(q.device).data_ptr(),
                                                 q.shape[0], kv_layer.shape[0], tiles.shape[0], nq, nkv, d,
                                                 block_table.shape[-1], page_size, mask_kind, mask_span, float(scale),
-                                                _stream()), "sharpi_attention_prefill_tc")
+                                                float(softcap), _ptr(sinks), _stream()), "sharpi_attention_prefill_tc")
 
 
 def gemm_nt(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
@@ -742,12 +773,18 @@ def moe_sort(expert_id: torch.Tensor, num_experts: int):
     return offsets, sorted_rows
 
 
+ROUTER_SCORING = {"sigmoid": 0, "softmax_chosen": 1}
+
+
 def router_topk(h32: torch.Tensor, router_weight: torch.Tensor, k: int, *, correction: Optional[torch.Tensor] = None,
-                scale: float = 1.0, renormalize: bool = False, want_scores: bool = False):
+                scale: float = 1.0, renormalize: bool = False, want_scores: bool = False,
+                bias: Optional[torch.Tensor] = None, scoring: str = "sigmoid"):
     """Sigmoid routing to ``k`` experts a row.  ``s = sigmoid(h . Wr^T)`` in float32; the ``k`` largest of
     ``s + correction`` are chosen (the lowest index among equals); the weights are ``scale * s`` of the chosen,
-    divided by their sum first when ``renormalize``.  Returns ``(expert_id int32 [T, k], weight float32 [T, k],
-    scores [T, E] or None)``."""
+    divided by their sum first when ``renormalize``.  ``bias`` float32 ``[E]`` is added to the logits.
+    ``scoring="softmax_chosen"``: the ``k`` largest logits are chosen and the weights are ``scale`` times the softmax
+    over the chosen logits alone (``scores`` are then the logits).  Returns ``(expert_id int32 [T, k], weight float32
+    [T, k], scores [T, E] or None)``."""
     _need(h32, "h32", torch.float32)
     _need(router_weight, "router_weight", torch.float32)
     T, H = h32.shape
@@ -760,12 +797,18 @@ def router_topk(h32: torch.Tensor, router_weight: torch.Tensor, k: int, *, corre
             raise KernelError(f"correction has {correction.numel()} entries for {E} experts")
     if not (1 <= k <= min(E, 32)):
         raise KernelError(f"experts per row must be 1 .. min(experts, 32), found {k} of {E}")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != E:
+            raise KernelError(f"router bias has {bias.numel()} entries for {E} experts")
+    if scoring not in ROUTER_SCORING:
+        raise KernelError(f"router scoring '{scoring}' is not one of {', '.join(ROUTER_SCORING)}")
     expert = torch.empty((T, k), dtype=torch.int32, device=h32.device)
     weight = torch.empty((T, k), dtype=torch.float32, device=h32.device)
     scores = torch.empty((T, E), dtype=torch.float32, device=h32.device) if want_scores else None
     check(kernel("sharpi_router_topk")(h32.data_ptr(), router_weight.data_ptr(), _ptr(correction), T, H, E, k,
                                        float(scale), int(renormalize), expert.data_ptr(), weight.data_ptr(),
-                                       _ptr(scores), _stream()), "sharpi_router_topk")
+                                       _ptr(scores), _ptr(bias), ROUTER_SCORING[scoring], _stream()), "sharpi_router_topk")
     return expert, weight, scores
 
 
@@ -1260,16 +1303,18 @@ def latent_down_post(down: torch.Tensor, *, q_rank: int, rank: int, rot: int, ro
                      q_norm_weight: Optional[torch.Tensor], c_norm_weight: torch.Tensor, eps: float,
                      positions: torch.Tensor, row_req: torch.Tensor, block_table: torch.Tensor,
                      inv_freq: Optional[torch.Tensor], kv_layer: torch.Tensor, page_size: int,
-                     write_kv: bool = True) -> torch.Tensor:
+                     write_kv: bool = True, rot_amplitude: float = 1.0) -> torch.Tensor:
     """Behind the fused down projection ``down`` float32 ``[T, q_rank + rank + rot]`` of latent attention: the normed
     query latent ``[T, q_rank]`` in the cache's dtype (returned), and ``[c | k_rot | 0]`` written into every row's
-    place in ``kv_layer [pages, planes, 1, page_size, D]`` (``[c | 0]`` into the value plane when there are two)."""
-    _need(down, "down", torch.float32)
+    place in ``kv_layer [pages, planes, 1, page_size, D]`` (``[c | 0]`` into the value plane when there are two).
+    ``down`` may be a column range of a wider product (rows apart); ``rot_amplitude`` multiplies the rotation's
+    cosines and sines."""
+    ld = _need_columns(down, "down", torch.float32)
     _need(c_norm_weight, "c_norm_weight", torch.float32)
     _need(kv_layer, "kv_layer")
-    T, ld = down.shape
+    T = down.shape[0]
     planes, D = int(kv_layer.shape[1]), int(kv_layer.shape[-1])
-    if tuple(kv_layer.shape[1:]) != (planes, 1, page_size, D) or ld != q_rank + rank + rot:
+    if tuple(kv_layer.shape[1:]) != (planes, 1, page_size, D) or down.shape[1] != q_rank + rank + rot:
         raise KernelError(f"kv_layer {tuple(kv_layer.shape)} or the projection's width {ld} disagree with the sizes")
     if inv_freq is not None:
         _need(inv_freq, "inv_freq", torch.float32)
@@ -1280,47 +1325,58 @@ def latent_down_post(down: torch.Tensor, *, q_rank: int, rank: int, rot: int, ro
                                             _ptr(q_norm_weight), c_norm_weight.data_ptr(), float(eps), positions.data_ptr(),
                                             row_req.data_ptr(), block_table.data_ptr(), block_table.shape[-1], page_size,
                                             _ptr(inv_freq), cq.data_ptr(), kv_layer.data_ptr(), planes, D, int(write_kv),
-                                            dtype_code(kv_layer.dtype), T, _stream()), "sharpi_latent_down_post")
+                                            dtype_code(kv_layer.dtype), T, float(rot_amplitude), _stream()),
+          "sharpi_latent_down_post")
     return cq
 
 
 def head_major(src: torch.Tensor, *, heads: int, stride: int, col0: int, n: int, out_dtype: torch.dtype) -> torch.Tensor:
     """Columns ``[col0, col0 + n)`` of every head of ``src [T, heads * stride]`` as ``[heads * T, n]`` (head by head,
-    the rows of a head in order) in ``out_dtype``: the operand of a product with one weight a head."""
-    _need(src, "src")
+    the rows of a head in order) in ``out_dtype``: the operand of a product with one weight a head.  ``src`` may be a
+    column range of a wider tensor."""
+    ld = _need_columns(src, "src")
     T = src.shape[0]
     if src.shape[1] != heads * stride:
         raise KernelError(f"src is {tuple(src.shape)}, expected [T, {heads} * {stride}]")
     out = torch.empty((heads * T, n), dtype=out_dtype, device=src.device)
     check(kernel("sharpi_head_major")(src.data_ptr(), dtype_code(src.dtype), T, heads, stride, col0, n, out.data_ptr(),
-                                      dtype_code(out_dtype), _stream()), "sharpi_head_major")
+                                      dtype_code(out_dtype), ld, _stream()), "sharpi_head_major")
     return out
 
 
-def head_minor(src: torch.Tensor, *, heads: int, out_dtype: torch.dtype) -> torch.Tensor:
-    """``src`` float32 ``[heads * T, n]`` (head by head) as ``[T, heads * n]`` in ``out_dtype``."""
+def head_minor(src: torch.Tensor, *, heads: int, out_dtype: torch.dtype, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``src`` float32 ``[heads * T, n]`` (head by head) as ``[T, heads * n]`` in ``out_dtype``.  ``gate`` float32
+    ``[T, heads]`` (possibly a column range of a wider product): head ``h`` of row ``t`` is multiplied by
+    ``sigmoid(gate[t, h])``."""
     _need(src, "src", torch.float32)
     n = src.shape[1]
     T = src.shape[0] // heads
+    gate_ld = 0
+    if gate is not None:
+        gate_ld = _need_columns(gate, "gate", torch.float32)
+        if tuple(gate.shape) != (T, heads):
+            raise KernelError(f"gate is {tuple(gate.shape)}, expected [{T}, {heads}]")
     out = torch.empty((T, heads * n), dtype=out_dtype, device=src.device)
-    check(kernel("sharpi_head_minor")(src.data_ptr(), T, heads, n, 0, n, out.data_ptr(), dtype_code(out_dtype), _stream()),
-          "sharpi_head_minor")
+    check(kernel("sharpi_head_minor")(src.data_ptr(), T, heads, n, 0, n, out.data_ptr(), dtype_code(out_dtype),
+                                      _ptr(gate), gate_ld, _stream()), "sharpi_head_minor")
     return out
 
 
 def latent_q_join(qa: torch.Tensor, q: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor], *,
-                  heads: int, dim: int, rank: int, rot: int, rot_dims: int, D: int, out_dtype: torch.dtype) -> torch.Tensor:
+                  heads: int, dim: int, rank: int, rot: int, rot_dims: int, D: int, out_dtype: torch.dtype,
+                  rot_amplitude: float = 1.0) -> torch.Tensor:
     """The query rows of latent attention, ``[T, heads, D]``: ``[qa[h, t] | rotate(q[t, h, dim:]) | 0]`` with ``qa``
-    float32 ``[heads * T, rank]`` (head by head) and ``q`` float32 ``[T, heads * (dim + rot)]``."""
+    float32 ``[heads * T, rank]`` (head by head) and ``q`` float32 ``[T, heads * (dim + rot)]`` (possibly a column range
+    of a wider product); ``rot_amplitude`` multiplies the rotation's cosines and sines."""
     _need(qa, "qa", torch.float32)
-    _need(q, "q", torch.float32)
+    ldq = _need_columns(q, "q", torch.float32)
     T = q.shape[0]
     if q.shape[1] != heads * (dim + rot) or tuple(qa.shape) != (heads * T, rank):
         raise KernelError(f"q {tuple(q.shape)} or qa {tuple(qa.shape)} disagree with the sizes")
     out = torch.empty((T, heads, D), dtype=out_dtype, device=q.device)
     check(kernel("sharpi_latent_q_join")(qa.data_ptr(), q.data_ptr(), positions.data_ptr(), _ptr(inv_freq), T, heads, dim,
                                          rank, rot, rot_dims if inv_freq is not None else 0, D, out.data_ptr(),
-                                         dtype_code(out_dtype), _stream()), "sharpi_latent_q_join")
+                                         dtype_code(out_dtype), ldq, float(rot_amplitude), _stream()), "sharpi_latent_q_join")
     return out
 
 
@@ -1364,12 +1420,76 @@ def gated_group_norm(y: torch.Tensor, proj: torch.Tensor, col_z: int, weight: to
 
 
 def sigmoid_gate(o: torch.Tensor, g: torch.Tensor) -> torch.Tensor:
-    """``o * sigmoid(g)`` element by element: ``o`` in the activation dtype, ``g`` float32 of the same shape."""
+    """``o * sigmoid(g)`` element by element: ``o [rows, cols]`` in the activation dtype, ``g`` float32 of the same
+    shape (possibly a column range of a wider product)."""
     _need(o, "o")
-    _need(g, "g", torch.float32)
+    g_ld = _need_columns(g, "g", torch.float32)
     if o.shape != g.shape:
         raise KernelError(f"shapes differ: {tuple(o.shape)}, {tuple(g.shape)}")
     out = torch.empty_like(o)
-    check(kernel("sharpi_sigmoid_gate")(o.data_ptr(), g.data_ptr(), out.data_ptr(), dtype_code(o.dtype), o.numel(), _stream()),
-          "sharpi_sigmoid_gate")
+    check(kernel("sharpi_sigmoid_gate")(o.data_ptr(), g.data_ptr(), out.data_ptr(), dtype_code(o.dtype), o.numel(),
+                                        int(o.shape[1]), g_ld, _stream()), "sharpi_sigmoid_gate")
     return out
+
+
+def add_layernorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, bias: Optional[torch.Tensor],
+                  eps: float, out_dtype: torch.dtype, *, rows: Optional[torch.Tensor] = None, want_fp32: bool = False):
+    """Residual add fused with a layer norm, ``(x - mean) / sqrt(var + eps) * w + b`` with ``var`` the mean of the
+    squared deviations.  The interface of :func:`add_rmsnorm`: without ``rows`` ``x += delta`` in place, with ``rows``
+    the gathered rows and ``x`` stays.  Returns ``(out, out32)``."""
+    _need(x, "x", torch.float32)
+    _need(weight, "weight", torch.float32)
+    H = x.shape[-1]
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    if weight.numel() != H or (bias is not None and bias.numel() != H):
+        raise KernelError(f"weight or bias disagree with the width {H}")
+    if delta is not None:
+        _need(delta, "delta", torch.float32)
+        if delta.shape != x.shape:
+            raise KernelError(f"delta shape {tuple(delta.shape)} differs from x shape {tuple(x.shape)}")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        T = rows.numel()
+    else:
+        T = x.numel() // H
+    out = torch.empty((T, H), dtype=out_dtype, device=x.device)
+    out32 = None
+    if want_fp32:
+        out32 = out if out_dtype == torch.float32 else torch.empty((T, H), dtype=torch.float32, device=x.device)
+    alias = out32 is not None and out32.data_ptr() == out.data_ptr()
+    check(kernel("sharpi_add_layernorm")(x.data_ptr(), _ptr(delta), weight.data_ptr(), _ptr(bias), float(eps), _ptr(rows),
+                                         T, H, out.data_ptr(), dtype_code(out_dtype), None if alias else _ptr(out32),
+                                         _stream()), "sharpi_add_layernorm")
+    return out, out32
+
+
+def qkv_post_wide(qkv: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor, block_table: torch.Tensor,
+                  q_out: torch.Tensor, kv_layer: torch.Tensor, *, nq: int, nkv: int, d: int, page_size: int,
+                  q_weight: torch.Tensor, k_weight: Optional[torch.Tensor], eps: float, q_count: int, k_count: int,
+                  temp_coef: float, temp_every: float, write_kv: bool, has_kv: bool) -> None:
+    """Behind a fused projection ``qkv`` float32 ``[T, (nq + 2 nkv) d]`` (or ``[T, nq d]`` when ``has_kv`` is false: the
+    layer reads another layer's cache): q as a whole is divided by its root mean square (``sqrt(sum / q_count + eps)``)
+    and multiplied by ``q_weight [nq d]``, k likewise with ``k_weight``; q also by ``1 + temp_coef * ln(1 + floor((pos +
+    1) / temp_every))`` when ``temp_every > 0``; q goes to ``q_out [T, nq, d]``, k and v into ``kv_layer [pages, 2, nkv,
+    page_size, d]`` at every row's position."""
+    ld = _need_columns(qkv, "qkv", torch.float32)
+    _need(q_out, "q_out")
+    _need(kv_layer, "kv_layer", q_out.dtype)
+    _need(q_weight, "q_weight", torch.float32)
+    T = positions.numel()
+    width = (nq + 2 * nkv) * d if has_kv else nq * d
+    if tuple(qkv.shape) != (T, width) or q_weight.numel() != nq * d:
+        raise KernelError(f"qkv {tuple(qkv.shape)} is not [{T}, {width}] or the q weight has {q_weight.numel()} entries")
+    if has_kv:
+        _need(k_weight, "k_weight", torch.float32)
+        if k_weight.numel() != nkv * d:
+            raise KernelError(f"the k weight has {k_weight.numel()} entries, expected {nkv * d}")
+    if tuple(kv_layer.shape[1:]) != (2, nkv, page_size, d):
+        raise KernelError(f"kv_layer shape {tuple(kv_layer.shape)} is not [pages, 2, {nkv}, {page_size}, {d}]")
+    check(kernel("sharpi_qkv_post_wide")(qkv.data_ptr(), ld, positions.data_ptr(), row_req.data_ptr(),
+                                         block_table.data_ptr(), q_weight.data_ptr(), _ptr(k_weight), float(eps),
+                                         int(q_count), int(k_count), q_out.data_ptr(), kv_layer.data_ptr(),
+                                         dtype_code(q_out.dtype), T, nq, nkv, d, block_table.shape[-1], page_size,
+                                         float(temp_coef), float(temp_every), int(write_kv), int(has_kv), _stream()),
+          "sharpi_qkv_post_wide")

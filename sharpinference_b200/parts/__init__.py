@@ -2,9 +2,9 @@
 from .base import (Block, CacheSpec, FeedForward, LayerSlot, Mixer, Norm, Part, PositionEncoding, StateSpec,
                    StepContext, StreamOp, make_part, part_kinds, register_part)
 from .linear import GroupedLinear, Linear
-from .norm import DynamicTanh, L2Norm, RMSNorm
+from .norm import DynamicTanh, L2Norm, LayerNorm, RMSNorm
 from .position import (NoPositionEncoding, RotaryEncoding, leading_rotary_inv_freq, partial_rotary_inv_freq,
-                       rotary_inv_freq)
+                       rotary_inv_freq, yarn_inv_freq)
 from .attention import PagedAttention, distance_bias_table, distance_bucket
 from .latent import LatentAttention
 from .mlstm import MLSTMMixer, fused_mlstm_columns
@@ -21,4 +21,4 @@ __all__ = ["Block", "CacheSpec", "FeedForward", "LayerSlot", "Mixer", "Norm", "P
            "DenseSwiGLU", "MoESigmoidTop1", "PreNormBlock", "StreamOp", "partial_rotary_inv_freq", "MLSTMMixer",
            "fused_mlstm_columns", "DenseMLP", "MoESigmoidTopK", "ParallelBlock", "ReinjectInput", "GroupRMSNorm",
            "HyperBlock", "PairEmbedding", "WKVMixer", "BranchPair", "SelectiveScanMixer", "leading_rotary_inv_freq", "DynamicTanh", "LatentAttention", "MoESigmoidTopKGated", "StateSpaceDualityMixer",
-           "ssd_projection_order", "distance_bias_table", "distance_bucket"]
+           "ssd_projection_order", "distance_bias_table", "distance_bucket", "LayerNorm", "yarn_inv_freq"]

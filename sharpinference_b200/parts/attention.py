@@ -17,6 +17,12 @@ projection, and a page holds keys only), a sliding window that keeps a sequence'
 (``distance_bias``, a table by distance built with :func:`distance_bias_table`), and a sigmoid gate on the
 concatenated heads before the output projection (``gate``).
 
+And: a q/k norm over the whole projection (``wide_norm``: all heads of q side by side are divided by their common
+root mean square and multiplied by a weight of that size, and so is k), a cap on the scaled score
+(``softcap``: ``s -> softcap * tanh(s / softcap)``), a learned sink per head whose exponential joins the softmax's
+denominator without a key or a value (``sinks``), a layer that brings queries only and reads the keys and values
+another layer cached (``borrows_kv``), and the gate's rows riding in the fused projection (``gate_fused``).
+
 Unequal key and value sizes: the kernels and the pages know one head size, so the part pads both to a common
 size D once, when it is built: zero rows in the fused projection (a padded q, k or v element is an exact zero),
 zero columns in the output projection.  Zeros change neither a score nor a rotation (the padded pairs get
@@ -113,13 +119,20 @@ def distance_bias_table(rel: torch.Tensor, far: int) -> torch.Tensor:
     return rel.to(torch.float32)[index].contiguous()
 
 
+def _pad_head_rows(block: torch.Tensor, heads: int, size: int, D: int) -> torch.Tensor:
+    """``block [heads * size, ...]`` with zero rows behind each head up to ``D`` rows a head."""
+    if size == D:
+        return block
+    wide = torch.zeros((heads, D) + tuple(block.shape[1:]), dtype=block.dtype, device=block.device)
+    wide[:, :size] = block.reshape((heads, size) + tuple(block.shape[1:]))
+    return wide.reshape((heads * D,) + tuple(block.shape[1:]))
+
+
 def _pad_projections(qkv: Linear, out: Linear, nq: int, nkv: int, dk: int, dv: int, D: int):
     """The fused q|k|v projection and the output projection with every head padded to ``D`` elements: zero rows
     (and zero bias entries) behind each head of q, k and v, zero columns behind each head in ``out``."""
     def pad_rows(block: torch.Tensor, heads: int, size: int) -> torch.Tensor:
-        wide = torch.zeros((heads, D) + tuple(block.shape[1:]), dtype=block.dtype, device=block.device)
-        wide[:, :size] = block.reshape((heads, size) + tuple(block.shape[1:]))
-        return wide.reshape((heads * D,) + tuple(block.shape[1:]))
+        return _pad_head_rows(block, heads, size, D)
 
     def pad_qkv(t: torch.Tensor) -> torch.Tensor:
         q, k, v = t[: nq * dk], t[nq * dk: (nq + nkv) * dk], t[(nq + nkv) * dk:]
@@ -143,7 +156,10 @@ class PagedAttention(Mixer):
                  softmax_scale: Optional[float] = None, act_dtype: torch.dtype = torch.bfloat16,
                  value_dim: Optional[int] = None, value_position: Optional[PositionEncoding] = None,
                  k_norm: Optional[Norm] = None, values_are_keys: bool = False, keep_first: int = 0,
-                 distance_bias: Optional[torch.Tensor] = None, gate: Optional[Linear] = None):
+                 distance_bias: Optional[torch.Tensor] = None, gate: Optional[Linear] = None,
+                 wide_norm: Optional[Tuple[torch.Tensor, Optional[torch.Tensor], float]] = None,
+                 softcap: float = 0.0, sinks: Optional[torch.Tensor] = None, borrows_kv: bool = False,
+                 gate_fused: bool = False):
         """``qk_norm``: any :class:`Norm` over the head size, applied to every head of q and k; after the
         position encoding (Llama 4's order) unless ``qk_norm_first``.  The weightless L2 norm after a rotation
         runs inside the kernel that rotates and writes the cache; every other combination applies the norm as
@@ -163,7 +179,27 @@ class PagedAttention(Mixer):
         ``distance_bias``: float32 ``[n + 1, heads]`` added to the scaled score by distance
         (:func:`distance_bias_table`).  ``gate``: a projection of the mixer's input whose sigmoid multiplies the
         concatenated heads.  A layer with kept positions or a distance bias, or with keys-only pages, runs the
-        general attention kernel."""
+        general attention kernel.
+
+        ``wide_norm = (q_weight [heads * head_dim], k_weight [kv_heads * head_dim] or None, eps)``: the q/k norm over
+        the whole projection, in one kernel with the temperature factor and the cache write (no position encoding
+        then).  ``softcap``, ``sinks`` (float32 ``[heads]``): see the module text.  ``borrows_kv``: ``qkv`` holds the
+        query rows only, and every schedule entry of the layer reads another entry's cache (``cache_from``); built
+        for the whole-projection path.  ``gate_fused``: the gate's ``heads * value_dim`` rows are the last rows of
+        ``qkv`` instead of a projection of their own."""
+        self.softcap, self.sinks = float(softcap), sinks
+        self.borrows_kv, self.gate_fused, self.wide_norm = bool(borrows_kv), bool(gate_fused), None
+        if sinks is not None and sinks.numel() != num_heads:
+            raise ValueError(f"sinks has {sinks.numel()} entries for {num_heads} heads")
+        if (self.softcap > 0.0 or sinks is not None) and values_are_keys:
+            raise ValueError("a score cap or sinks are not built for attention whose values are its keys")
+        if position is not None and getattr(position, "amplitude", 1.0) != 1.0:
+            raise ValueError("a rotation with an amplitude is not built for this mixer")
+        if wide_norm is not None or borrows_kv or gate_fused:
+            self._init_wide(qkv, out, num_heads, num_kv_heads, head_dim, mask, span, position, qk_norm, temperature,
+                            softmax_scale, act_dtype, value_dim, value_position, values_are_keys, keep_first,
+                            distance_bias, gate, wide_norm)
+            return
         if num_heads % num_kv_heads != 0:
             raise ValueError(f"heads ({num_heads}) must be a multiple of kv heads ({num_kv_heads})")
         key_dim = head_dim
@@ -256,6 +292,98 @@ class PagedAttention(Mixer):
         # an encoding that edits q and k itself may look at the step's host-side lists: no graph then
         self.graph_safe = position is None or position.rotary() is not None
 
+    def _init_wide(self, qkv, out, num_heads, num_kv_heads, head_dim, mask, span, position, qk_norm, temperature,
+                   softmax_scale, act_dtype, value_dim, value_position, values_are_keys, keep_first, distance_bias, gate,
+                   wide_norm) -> None:
+        """The layer whose q/k norm runs over the whole projection."""
+        nq, nkv, dk = num_heads, num_kv_heads, head_dim
+        dv = dk if value_dim is None else int(value_dim)
+        if wide_norm is None:
+            raise ValueError("a layer that borrows keys and values, or carries its gate in the fused projection, is built "
+                             "with the q/k norm over the whole projection (wide_norm)")
+        if position is not None or value_position is not None or qk_norm is not None or values_are_keys:
+            raise ValueError("the norm over the whole projection comes without position encoding, per-head norm or "
+                             "values that are the keys")
+        if nq % nkv != 0 or min(dk, dv) <= 0 or max(dk, dv) > 512:
+            raise ValueError(f"heads ({nq}) must be a multiple of kv heads ({nkv}), head sizes ({dk}, {dv}) 1 .. 512")
+        if keep_first and mask != "window":
+            raise ValueError("kept first positions belong to the window mask")
+        wq, wk, eps = wide_norm
+        kv_rows = 0 if self.borrows_kv else nkv * (dk + dv)
+        g_rows = nq * dv if self.gate_fused else 0
+        if self.gate_fused and gate is not None:
+            raise ValueError("the gate is either a projection of its own or part of the fused projection")
+        if qkv.out_features != nq * dk + kv_rows + g_rows:
+            raise ValueError(f"the fused projection has {qkv.out_features} rows, expected {nq * dk + kv_rows + g_rows} "
+                             f"(queries {nq * dk}, keys and values {kv_rows}, gate {g_rows})")
+        if qkv.bias is not None:
+            raise ValueError("the whole-projection path takes a projection without bias")
+        if out.in_features != nq * dv:
+            raise ValueError(f"output projection reads {out.in_features} columns, expected {nq * dv}")
+        if gate is not None and gate.out_features != nq * dv:
+            raise ValueError(f"the gate has {gate.out_features} rows, expected heads * value_dim = {nq * dv}")
+        if wq.numel() != nq * dk or (not self.borrows_kv and (wk is None or wk.numel() != nkv * dk)):
+            raise ValueError("the norm weights disagree with the sizes of q or k")
+        if distance_bias is not None and (distance_bias.dim() != 2 or distance_bias.shape[1] != nq):
+            raise ValueError(f"the distance bias is {tuple(distance_bias.shape)}, expected [distances, {nq}]")
+        D = dk
+        if dk != dv:            # pages and kernels know one head size: pad both with zeros, once
+            D = max(dk, dv)
+            D = (D + 15) // 16 * 16 if D <= 128 else D + (D & 1)
+            w = qkv.weight
+            parts = [_pad_head_rows(w[: nq * dk], nq, dk, D)]
+            at = nq * dk
+            if not self.borrows_kv:
+                parts.append(_pad_head_rows(w[at: at + nkv * dk], nkv, dk, D))
+                parts.append(_pad_head_rows(w[at + nkv * dk: at + nkv * (dk + dv)], nkv, dv, D))
+                at += nkv * (dk + dv)
+            if self.gate_fused:
+                parts.append(_pad_head_rows(w[at:], nq, dv, D))
+            qkv = Linear(torch.cat(parts).contiguous(), qkv.name, stream_rows=qkv.stream_rows)
+            ow = out.weight
+            wide = torch.zeros((ow.shape[0], nq, D), dtype=ow.dtype, device=ow.device)
+            wide[:, :, :dv] = ow.reshape(ow.shape[0], nq, dv)
+            out = Linear(wide.reshape(ow.shape[0], nq * D).contiguous(), out.name, stream_rows=out.stream_rows,
+                         bias=out.bias, split_add_rows=out.split_add_rows)
+            if gate is not None:
+                gate = Linear(_pad_head_rows(gate.weight, nq, dv, D).contiguous(), gate.name,
+                              bias=None if gate.bias is None else _pad_head_rows(gate.bias, nq, dv, D).contiguous())
+            wq = _pad_head_rows(wq, nq, dk, D).contiguous()
+            wk = None if wk is None else _pad_head_rows(wk, nkv, dk, D).contiguous()
+        self.wide_norm = (wq, wk, float(eps))
+        self.qkv, self.out, self.gate = qkv, out, gate
+        self.key_dim, self.value_dim, self.head_dim = dk, dv, D
+        self.num_heads, self.num_kv_heads = nq, nkv
+        self.cache_spec = CacheSpec(mask, span if mask != "full" else 0, nkv, D, planes=2, keep_first=int(keep_first))
+        self.values_are_keys, self.keep_first, self.distance_bias = False, int(keep_first), distance_bias
+        self._general_attention = self.keep_first > 0 or distance_bias is not None
+        self._general = False
+        self.position = self.value_position = self.qk_norm = self.k_norm = None
+        self.qk_norm_first, self._norm_fused, self._ones = False, False, None
+        self.temperature = temperature
+        self.softmax_scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(dk)
+        self.act_dtype = act_dtype
+        self.graph_safe = True
+
+    def _forward_wide(self, ctx: StepContext, slot: LayerSlot, plan, table, qkv: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+        T, nq, nkv, d = ctx.num_tokens, self.num_heads, self.num_kv_heads, self.head_dim
+        if self.borrows_kv and slot.writes_cache:
+            raise ValueError("a layer that brings queries only must read another entry's cache (cache_from)")
+        wq, wk, eps = self.wide_norm
+        coef, every = self.temperature if self.temperature is not None else (0.0, 0.0)
+        first = nq * d + (0 if self.borrows_kv else 2 * nkv * d)
+        q = torch.empty((T, nq, d), dtype=self.act_dtype, device=qkv.device)
+        ops.qkv_post_wide(qkv[:, :first], ctx.positions, ctx.row_request, table, q, slot.kv, nq=nq, nkv=nkv, d=d,
+                          page_size=slot.page_size, q_weight=wq, k_weight=wk, eps=eps, q_count=nq * self.key_dim,
+                          k_count=nkv * self.key_dim, temp_coef=coef, temp_every=every, write_kv=slot.writes_cache,
+                          has_kv=not self.borrows_kv)
+        o = self._attend(ctx, slot, plan, table, q)
+        if self.gate_fused:
+            o = ops.sigmoid_gate(o.view(T, -1), qkv[:, first:])
+        elif self.gate is not None:
+            o = ops.sigmoid_gate(o.view(T, -1), self.gate(h))
+        return self.out(o)
+
     def prefill_tile_rows(self, page_size: int) -> int:
         """Rows of one request that one attention CTA serves in a prompt portion: 128 where the tcgen05
         kernel takes this layer (bfloat16, head size 64 or 128, pages of 64 * 2^k), else 64."""
@@ -281,6 +409,8 @@ class PagedAttention(Mixer):
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         table = ctx.block_tables[slot.group]
         qkv = self.qkv(h)                                                       # [T, (nq + 2 nkv) d] float32
+        if self.wide_norm is not None:
+            return self._forward_wide(ctx, slot, plan, table, qkv, h)
         if self._general:
             return self._forward_general(ctx, slot, plan, table, qkv, h)
 
@@ -353,12 +483,14 @@ class PagedAttention(Mixer):
             if plan.num_tiles:
                 prefill = ops.attention_prefill_tc if plan.tile_rows == ops.TC_PREFILL_TILE else ops.attention_prefill
                 prefill(q, slot.kv, table, plan.tiles, o, nq=nq, nkv=nkv, d=d, page_size=slot.page_size,
-                        mask_kind=mask_kind, mask_span=mask_span, scale=self.softmax_scale)
+                        mask_kind=mask_kind, mask_span=mask_span, scale=self.softmax_scale, softcap=self.softcap,
+                        sinks=self.sinks)
             if plan.num_decode_rows:
                 ops.attention_decode(q, slot.kv, table, ctx.row_request, ctx.positions, o, rows=plan.decode_rows,
                                      num_rows=plan.num_decode_rows, nq=nq, nkv=nkv, d=d, page_size=slot.page_size,
                                      mask_kind=mask_kind, mask_span=mask_span, scale=self.softmax_scale,
-                                     max_context=ctx.max_context, max_keys=plan.decode_keys)
+                                     max_context=ctx.max_context, max_keys=plan.decode_keys, softcap=self.softcap,
+                                     sinks=self.sinks)
         elif self.values_are_keys and ops.keys_attention_supported(self.act_dtype, d, d):
             # keys-only pages: the tensor-core kernels that read a key once for scores and value sum
             o = torch.empty((T, nq * d), dtype=torch.bfloat16, device=h.device)
@@ -373,5 +505,5 @@ class PagedAttention(Mixer):
             o = ops.paged_attention_generic(q, slot.kv, table, ctx.row_request, ctx.positions, nq=nq, nkv=nkv, d=d,
                                             page_size=slot.page_size, mask_kind=mask_kind, mask_span=mask_span,
                                             scale=self.softmax_scale, keep_first=self.keep_first,
-                                            dist_bias=self.distance_bias)
+                                            dist_bias=self.distance_bias, softcap=self.softcap, sinks=self.sinks)
         return o

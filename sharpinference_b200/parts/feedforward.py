@@ -274,6 +274,11 @@ class MoESigmoidTopKGated(FeedForward):
 
     With one expert a row this is the arithmetic of :class:`MoESigmoidTop1`, which fuses more and is what a builder
     should pick then; this part takes any ``top_k``.
+
+    Other routers of the same mixture, by argument: ``router_bias`` ``[E]`` is added to the logits;
+    ``scoring="softmax_chosen"`` picks the ``top_k`` largest logits and weights them by the softmax over the chosen
+    logits alone; ``weights_on="output"`` multiplies an expert's *output* by its weight (in the second grouped
+    product's epilogue) instead of its input.
     """
 
     wants_fp32_input = True
@@ -282,8 +287,16 @@ class MoESigmoidTopKGated(FeedForward):
 
     def __init__(self, *, router: torch.Tensor, experts_gate_up: GroupedLinear, experts_down: GroupedLinear, top_k: int,
                  shared: Optional[DenseSwiGLU] = None, renormalize: bool = False,
-                 act_dtype: torch.dtype = torch.bfloat16):
+                 act_dtype: torch.dtype = torch.bfloat16, router_bias: Optional[torch.Tensor] = None,
+                 scoring: str = "sigmoid", weights_on: str = "input"):
         E = experts_gate_up.num_groups
+        if scoring not in ops.ROUTER_SCORING:
+            raise ValueError(f"router scoring '{scoring}' is not one of {', '.join(ops.ROUTER_SCORING)}")
+        if weights_on not in ("input", "output"):
+            raise ValueError(f"weights_on '{weights_on}' is not one of input, output")
+        if router_bias is not None and router_bias.numel() != E:
+            raise ValueError(f"router bias has {router_bias.numel()} entries for {E} experts")
+        self.router_bias, self.scoring, self.weights_on = router_bias, scoring, weights_on
         if router.shape != (E, experts_gate_up.in_features):
             raise ValueError(f"router weight is {tuple(router.shape)}, expected [{E}, {experts_gate_up.in_features}]")
         if experts_down.num_groups != E or experts_gate_up.out_features != 2 * experts_down.in_features:
@@ -314,22 +327,31 @@ class MoESigmoidTopKGated(FeedForward):
                     self.shared.forward(ctx, h, out=base, accumulate=True)
                 else:
                     base = self.shared.forward(ctx, h)
-        expert, weight, _ = ops.router_topk(h32, self.router, k, renormalize=self.renormalize)
+        expert, weight, _ = ops.router_topk(h32, self.router, k, renormalize=self.renormalize, bias=self.router_bias,
+                                            scoring=self.scoring)
         if "router_choices" in ctx.extras:          # tracing: which experts every row went to
             ctx.extras["router_choices"].append(expert)
         offsets, sorted_pairs = ops.moe_sort(expert.view(-1), self.num_experts)     # pair = row * k + choice
         pair_rows = ops.moe_pair_tokens(sorted_pairs, k) if k > 1 else sorted_pairs
         y = torch.empty((T * k, self.experts_down.out_features), dtype=torch.float32, device=h.device)
+        # the weight scales gate and up before the nonlinearity (the expert's input), or the second product's rows
+        w_in = weight.view(-1) if self.weights_on == "input" else None
+        w_out = weight.view(-1) if self.weights_on == "output" else None
         if self._tensor_core and h.dtype == torch.bfloat16:
             h_sorted = ops.gather_rows_bf16(h, pair_rows)
             act = ops.tc_grouped_gemm(h_sorted, self.experts_gate_up.weight, offsets, mode=ops.TC_MODE_SWIGLU,
-                                      row_scale=weight.view(-1), scale_rows=sorted_pairs)
+                                      row_scale=w_in, scale_rows=sorted_pairs if w_in is not None else None)
             ops.tc_grouped_gemm(act, self.experts_down.weight, offsets, mode=ops.TC_MODE_STORE, out=y,
-                                out_rows=sorted_pairs)
+                                out_rows=sorted_pairs, row_scale=w_out,
+                                scale_rows=sorted_pairs if w_out is not None else None)
         else:
             gu = self.experts_gate_up(h, offsets, rows=T * k, a_rows=pair_rows)        # sorted order
-            act = ops.swiglu(gu, self.act_dtype, row_scale=weight.view(-1), scale_rows=sorted_pairs)
-            self.experts_down(act, offsets, rows=T * k, out_rows=sorted_pairs, out=y)
+            act = ops.swiglu(gu, self.act_dtype, row_scale=w_in, scale_rows=sorted_pairs if w_in is not None else None)
+            w_down = self.experts_down.weight
+            if w_down.dtype == torch.float32 and act.dtype != torch.float32:
+                act = act.to(torch.float32)
+            ops.gemm_nt(act, w_down, out=y, group_offsets=offsets, out_rows=sorted_pairs, rows=T * k,
+                        row_scale=w_out, scale_rows=sorted_pairs if w_out is not None else None)
         if side is not None:
             main.wait_stream(side)
         return ops.moe_combine(y, k, add=base, out=base)

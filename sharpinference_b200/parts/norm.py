@@ -1,5 +1,5 @@
-"""Norm parts: RMSNorm with a weight, the weightless L2 norm used on q and k per head, and the element-wise
-squashing norm (``DynamicTanh``).
+"""Norm parts: RMSNorm with a weight, the weightless L2 norm used on q and k per head, the element-wise
+squashing norm (``DynamicTanh``) and the layer norm with weight and bias (``LayerNorm``).
 
 RMSNorm: ``x * rsqrt(mean(x^2) + eps) * w`` (src/SharpInference.Cpu/SimdKernels.cs:4209-4246);
 the weightless form drops ``w`` (src/SharpInference.Cpu/SimdKernels.cs:4252-4283).  The sum of
@@ -7,6 +7,8 @@ squares, the rsqrt and the scaling are float32.  Models that store the weight ar
 ``1 + w`` pass ``unit_offset=True``: the sum is formed once, in float32, when the part is built.
 """
 from __future__ import annotations
+
+from typing import Optional
 
 import torch
 
@@ -51,3 +53,15 @@ class DynamicTanh(Norm):
 
     def apply(self, x, delta, *, rows=None, out_dtype=torch.bfloat16, want_fp32=False):
         return ops.add_dyt(x, delta, self.weight, self.bias, self.alpha, out_dtype, rows=rows, want_fp32=want_fp32)
+
+
+@register_part("norm", "layernorm")
+class LayerNorm(Norm):
+    """``(x - mean) / sqrt(var + eps) * w + b`` over the last axis, ``var`` the mean of the squared deviations from the
+    mean (formed in a second pass, so nothing cancels).  Float32; the residual add is fused as in the others."""
+
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float):
+        self.weight, self.bias, self.eps = weight, bias, float(eps)
+
+    def apply(self, x, delta, *, rows=None, out_dtype=torch.bfloat16, want_fp32=False):
+        return ops.add_layernorm(x, delta, self.weight, self.bias, self.eps, out_dtype, rows=rows, want_fp32=want_fp32)

@@ -79,12 +79,42 @@ def leading_rotary_inv_freq(rot_dims: int, base: float) -> torch.Tensor:
     return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / float(max(rot_dims, 1))).to(torch.float32)
 
 
+def yarn_inv_freq(rot_dims: int, base: float, factor: float, original: float, fast: float, slow: float):
+    """Frequencies and amplitude of a rotation whose long waves are stretched ("YaRN"): float32 ``[rot_dims / 2]`` and
+    a float.  With ``f_i = base^(-2i / rot_dims)`` and ``at(t) = rot_dims * ln(original / (2 pi t)) / (2 ln base)`` (the
+    pair whose wave makes ``t`` turns over ``original`` positions):
+
+        lo = max(floor(at(fast)), 0),  hi = min(ceil(at(slow)), rot_dims - 1)
+        ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)
+        frequency_i = f_i / factor * ramp_i + f_i * (1 - ramp_i)
+
+    so pairs below ``lo`` keep their frequency, pairs above ``hi`` are slowed by ``factor``, and the ones between are
+    blended.  Cosines and sines are multiplied by ``0.1 * ln(factor) + 1`` (the amplitude).  Formed in float64 and
+    rounded once."""
+    if rot_dims % 2 or rot_dims <= 0:
+        raise ValueError(f"rotated size {rot_dims} must be even and positive")
+    if not (factor > 0 and original > 0 and fast > 0 and slow > 0 and base > 1):
+        raise ValueError("factor, original, fast and slow must be positive and the base above 1")
+    i = torch.arange(rot_dims // 2, dtype=torch.float64)
+    f = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / float(rot_dims))
+
+    def at(turns: float) -> float:
+        return rot_dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(at(fast)), 0)
+    hi = min(math.ceil(at(slow)), rot_dims - 1)
+    ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return (f / factor * ramp + f * (1.0 - ramp)).to(torch.float32), 0.1 * math.log(factor) + 1.0
+
+
 @register_part("position", "rotary")
 class RotaryEncoding(PositionEncoding):
-    def __init__(self, inv_freq: torch.Tensor, pairing: str = "interleaved", rot_dims: Optional[int] = None):
+    def __init__(self, inv_freq: torch.Tensor, pairing: str = "interleaved", rot_dims: Optional[int] = None,
+                 amplitude: float = 1.0):
         """``rot_dims``: only the first ``rot_dims`` elements of a head are turned, paired among themselves
         (``halves``: ``(i, i + rot_dims / 2)``; ``interleaved``: ``(2i, 2i + 1)``), and ``inv_freq`` has
-        ``rot_dims / 2`` entries; None: the whole head, ``inv_freq`` of half the head size."""
+        ``rot_dims / 2`` entries; None: the whole head, ``inv_freq`` of half the head size.  ``amplitude``
+        multiplies every cosine and sine (:func:`yarn_inv_freq`); the mixers that take it say so."""
         if pairing not in ("interleaved", "halves"):
             raise ValueError(f"rotary pairing '{pairing}' is not one of interleaved, halves")
         if rot_dims is not None and (rot_dims % 2 or inv_freq.numel() != rot_dims // 2):
@@ -92,6 +122,7 @@ class RotaryEncoding(PositionEncoding):
         self.inv_freq = inv_freq
         self.pairing = pairing
         self.rot_dims = rot_dims
+        self.amplitude = float(amplitude)
 
     def rotary(self) -> Optional[Tuple[torch.Tensor, str]]:
         return self.inv_freq, self.pairing

@@ -74,4 +74,4 @@ def _ensure_builtin() -> None:
     global _builtin_loaded
     if not _builtin_loaded:
         _builtin_loaded = True
-        from .models import latinex, llama4, notedra, zaposun  # noqa: F401  (they register themselves)
+        from .models import gisilix, latinex, llama4, notedra, zaposun  # noqa: F401  (they register themselves)
