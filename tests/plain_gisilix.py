@@ -171,12 +171,12 @@ def route(h, t, p, top):
 
 def mixture(h, mlp, t, p, round_to=None, choices=None):
     """``choices`` [n, top]: experts to use instead of the router's own (the weights are then the softmax over
-    those experts' logits)."""
+    those experts' logits).  Returns (output, chosen experts, router logits)."""
     top, E = mlp["router"]["top"], mlp["router"]["experts"]
+    z = h @ t[p + "router"].T + t[p + "router.b"]
     if choices is None:
         idx, w = route(h, t, p, top)
     else:
-        z = h @ t[p + "router"].T + t[p + "router.b"]
         idx = choices.to(torch.long)
         w = torch.softmax(torch.gather(z, 1, idx), dim=-1)
     hr = _r(h, round_to)
@@ -187,12 +187,12 @@ def mixture(h, mlp, t, p, round_to=None, choices=None):
             out[rows] += w[rows, slot].view(-1, 1) * gated(hr[rows], t, f"{p}e{e}.", round_to)
     if mlp.get("shared"):
         out = out + gated(hr, t, p + "shared.", round_to)
-    return out, idx
+    return out, idx, z
 
 
 def feed_forward(h, mlp, t, p, round_to=None, choices=None):
     if mlp["kind"] == "dense":
-        return gated(_r(h, round_to), t, p, round_to), None
+        return gated(_r(h, round_to), t, p, round_to), None, None
     return mixture(h, mlp, t, p, round_to, choices)
 
 
@@ -202,7 +202,8 @@ def feed_forward(h, mlp, t, p, round_to=None, choices=None):
 def forward(config: dict, tensors: Dict[str, torch.Tensor], tokens: List[int], round_to=None, layers_out=None,
             choices: Optional[List[torch.Tensor]] = None, choices_out: Optional[list] = None) -> torch.Tensor:
     """Logits [n, vocab] of one sequence from position 0.  ``layers_out``: a list that receives the residual stream
-    after every layer.  ``choices``: per mixture layer (in order) the experts to follow."""
+    after every layer.  ``choices``: per mixture layer (in order) the experts to follow.  ``choices_out``: a list
+    that receives, per mixture layer, (router logits [n, E], chosen experts [n, top])."""
     t = {k: (v.to(F64) if v.is_floating_point() else v) for k, v in tensors.items()}
     eps = config["norm"]["eps"]
     x = t["embed"][torch.tensor(tokens, dtype=torch.long)]
@@ -230,11 +231,33 @@ def forward(config: dict, tensors: Dict[str, torch.Tensor], tokens: List[int], r
             if layer["mlp"]["kind"] == "moe":
                 follow = choices[routed] if choices is not None else None
                 routed += 1
-            y, idx = feed_forward(h, layer["mlp"], t, p + "mlp.", round_to, follow)
+            y, idx, z = feed_forward(h, layer["mlp"], t, p + "mlp.", round_to, follow)
             if idx is not None and choices_out is not None:
-                choices_out.append(idx)
+                choices_out.append((z, idx))
             x = x + y
         if layers_out is not None:
             layers_out.append(x.clone())
     h = layer_norm(x, t["final.norm"], t["final.norm.b"], eps)
     return _r(h, round_to) @ t["embed"].T
+
+
+def load_folder(model_dir):
+    import json
+    import os
+
+    from safetensors.torch import load_file
+    with open(os.path.join(model_dir, "config.json")) as fh:
+        cfg = json.load(fh)
+    w = {k: (v.to(F64) if v.is_floating_point() else v) for k, v in
+         load_file(os.path.join(model_dir, "model.safetensors")).items()}
+    return cfg, w
+
+
+def generate_greedy(config, W, prompt, n):
+    toks, out = list(prompt), []
+    for _ in range(n):
+        nxt = int(torch.argmax(forward(config, W, toks)[-1]))
+        out.append(nxt)
+        toks.append(nxt)
+    return out
+
