@@ -76,7 +76,7 @@ CASE_A = top(97, 64, 1e-5, [
 # of three; no cap on one layer and no query factor on another; latent attention first.
 CASE_B = top(61, 52, 1e-4, [
     lat2(3, 10, 6, 10, 20, 0.8, (6, 50.0, None), 70, moe(3, 3, 12, 20)),
-    att(3, 3, 10, 10, 0.8, 0.0, (0.5, 3), None),
+    att(3, 3, 10, 10, 0.5, 0.0, (0.25, 3), None),
     lat2(2, 12, 4, 6, 14, 1.2, (2, 300.0, (2.0, 8, 2.0, 0.5)), 1, dense(30)),
     lat(2, 6, 10, 9, 1.5, None),
     lat2(1, 4, 2, 4, 7, 1.0, (2, 10.0, (8.0, 4, 1.0, 0.25)), 2, moe(5, 2, 10, 0)),
@@ -115,7 +115,7 @@ CASE_E = top(50, 96, 1e-5, [
 ])
 
 # config, std of the weights, seed
-CASES = {"A": (CASE_A, 0.15, 41), "B": (CASE_B, 0.18, 42), "C": (CASE_C, 0.1, 43), "D": (CASE_D, 0.5, 44),
+CASES = {"A": (CASE_A, 0.15, 41), "B": (CASE_B, 0.13, 42), "C": (CASE_C, 0.1, 43), "D": (CASE_D, 0.5, 44),
          "E": (CASE_E, 0.1, 45)}
 
 

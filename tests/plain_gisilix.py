@@ -120,7 +120,7 @@ def attention(h, m, t, p, eps, kv=None, round_to=None):
     if cap:
         s = cap * torch.tanh(s / cap)
     w = softmax_rows(s, causal(n), t[p + "sink"] if (p + "sink") in t else None)
-    o = torch.einsum("hij,jhd->ihd", _r(w, None), vh).reshape(n, H * dv)
+    o = _r(torch.einsum("hij,jhd->ihd", w, vh).reshape(n, H * dv), round_to)
     if (p + "g") in t:
         o = o * torch.sigmoid(h @ t[p + "g"].T)
     return _r(o, round_to) @ t[p + "o"].T
@@ -136,9 +136,11 @@ def latent_attention(h, m, t, p, eps, round_to=None):
     q = (h @ t[p + "q"].T).view(n, H, d + dr)
     down = h @ t[p + "dkv"].T
     c = _r(rms(down[:, :r], t[p + "dkv.norm"], eps), round_to)
-    k = (c @ t[p + "uk"].T).view(n, H, d)
+    # with ``round_to``: queries, keys and the heads' outputs are rounded once more, as an engine that stores them in
+    # that dtype between its products would
+    k = _r((c @ t[p + "uk"].T), round_to).view(n, H, d)
     v = (c @ t[p + "uv"].T).view(n, H, dv)
-    s = torch.einsum("ihd,jhd->hij", q[..., :d], k)
+    s = torch.einsum("ihd,jhd->hij", _r(q[..., :d], round_to), k)
     if dr:
         rot = m["rot"]
         f, amp = yarn_frequencies(rot["dims"], rot["base"], rot.get("scaling"))
@@ -148,7 +150,7 @@ def latent_attention(h, m, t, p, eps, round_to=None):
     s = s * m["scale"]
     window = (m.get("mask") or {}).get("size", 0)
     w = softmax_rows(s, causal(n, window))
-    o = torch.einsum("hij,jhd->ihd", w, v)
+    o = _r(torch.einsum("hij,jhd->ihd", w, v), round_to)
     if (p + "g") in t:
         o = o * torch.sigmoid(h @ t[p + "g"].T).view(n, H, 1)
     return _r(o.reshape(n, H * dv), round_to) @ t[p + "o"].T

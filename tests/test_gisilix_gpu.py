@@ -55,9 +55,12 @@ def engine_for(folder, dtype, max_tokens, max_batch=4, page_size=None, graphs=Tr
     return Engine(folder, dtype=dtype, device=DEV, options=opts)
 
 
-def reference_for(folder, reqs, routing, fallback, dtype):
+def reference_for(folder, reqs, routing, fallback, dtype, slack=None):
     """float32 runs are held to the plain logits as they are; bfloat16 runs to the plain logits under the engine's
-    own expert choices, each differing choice having to be a near-tie of the plain router's logits."""
+    own expert choices, each differing choice having to be a near-tie of the plain router's logits.  ``slack`` (a
+    dict) receives, per request, what rounding alone does to every position's logits in the plain model (the operands
+    of its matrix products rounded to bfloat16), relative to the request's largest logit: large score factors make
+    single positions sensitive, and a bfloat16 run is held to three times that where it exceeds the tolerance."""
     if dtype == "float32":
         return fallback
     cfg, w = plain.load_folder(folder)
@@ -71,7 +74,22 @@ def reference_for(folder, reqs, routing, fallback, dtype):
             assert float((kth - z.gather(1, forced)).max()) < MARGIN * max(1.0, float(z.abs().max())), \
                 f"request {rid}: an expert choice differs beyond a near-tie"
         ref[rid] = logits
+        if slack is not None:
+            rounded = plain.forward(cfg, w, toks, choices=choices, round_to=torch.bfloat16)
+            slack[rid] = (rounded - logits).abs().max(dim=-1).values / float(logits.abs().max())
     return ref
+
+
+def worst_excess(got, ref, tol, slack):
+    """The largest error over the wanted rows as a multiple of what the row is allowed: ``tol``, or three times what
+    rounding alone does at that position where that is more."""
+    worst, where = 0.0, None
+    for (rid, pos), row in got.items():
+        err = float((row.double() - ref[rid][pos]).abs().max()) / float(ref[rid].abs().max())
+        allowed = max(tol, 3.0 * float(slack[rid][pos])) if slack else tol
+        if not err / allowed <= worst:
+            worst, where = err / allowed, (rid, pos, err)
+    return worst, where
 
 
 def run_and_compare(folder, name, dtype, steps, expected, page_size=None, max_batch=4, reqs=None):
@@ -84,9 +102,10 @@ def run_and_compare(folder, name, dtype, steps, expected, page_size=None, max_ba
     assert not eng.cache.requests and all(g.pages.held_count == 0 for g in eng.cache.groups)
     wanted = sum(len(e["want"]) for st in steps for e in st["entries"])
     assert len({rid for rid, _ in got}) == len(reqs) and len(got) == wanted
-    ref = reference_for(folder, reqs, routing, expected[name] if expected else None, dtype)
-    err, where = traces.worst_error(got, ref)
-    assert err < TOL[dtype], f"{name} {dtype}: error {err} at {where}"
+    slack = {} if dtype == "bfloat16" else None
+    ref = reference_for(folder, reqs, routing, expected[name] if expected else None, dtype, slack)
+    excess, where = worst_excess(got, ref, TOL[dtype], slack)
+    assert excess < 1.0, f"{name} {dtype}: {excess} times the allowed error at {where}"
     return eng
 
 
@@ -536,9 +555,10 @@ def test_long_decoding_through_graphs(folders, name, dtype):
         assert eng.runner.graph_replays > 200
         ref = {rid: plain.forward(cfg, w, toks) for rid, toks in reqs.items()}
     else:
-        ref = reference_for(folders[name], reqs, routing, None, dtype)
-    err, where = traces.worst_error(got, ref)
-    assert err < TOL[dtype], (err, where)
+        slack = {}
+        ref = reference_for(folders[name], reqs, routing, None, dtype, slack)
+    excess, where = worst_excess(got, ref, TOL[dtype], slack if routing is not None else None)
+    assert excess < 1.0, (excess, where)
 
 
 @pytest.mark.parametrize("name", sorted(CASES))
