@@ -274,15 +274,16 @@ def main() -> int:
     ap.add_argument("--own-dense-rows", type=int, default=0,
                     help="EngineOptions.own_dense_rows: dense products of up to this many rows on the engine's own kernel")
     ap.add_argument("--points", default="1,64", help="further decode batch sizes, comma separated ('' for none)")
-    ap.add_argument("--widths", default="1024,2048,4096", help="--preset notedra / zaposun / latinex: the layer widths to measure")
-    ap.add_argument("--preset", default="scout", choices=["scout", "maverick", "long", "notedra", "zaposun", "latinex"],
+    ap.add_argument("--widths", default="1024,2048,4096", help="--preset notedra / zaposun / latinex / gisilix: the layer widths to measure")
+    ap.add_argument("--preset", default="scout", choices=["scout", "maverick", "long", "notedra", "zaposun", "latinex", "gisilix"],
                     help="scout: 20 Scout-sized layers, batch 8 at context 8192 (the default run); maverick: 4 "
                          "Maverick-sized layers (dense / 128 experts alternating), batch 64 at context 4096; long: 8 "
                          "Scout-sized layers, one 65536-token prompt prefilled in 2048-token portions, then 256 "
                          "decoded tokens; notedra: prefill and decode of the Notedra architecture at --widths beside "
                          "Llama 4 at equal width (bench_notedra.py), context 2048, batches --points; zaposun: the same for the "
                          "Zaposun architecture beside Notedra (bench_zaposun.py); latinex: the same for the Latinex architecture "
-                         "beside Notedra (bench_latinex.py)")
+                         "beside Notedra (bench_latinex.py); gisilix: the same for the Gisilix architecture beside Latinex "
+                         "(bench_gisilix.py)")
     ns = ap.parse_args()
     if ns.preset == "maverick":
         defaults = ap.parse_args([])
@@ -313,7 +314,8 @@ def main() -> int:
     cfg = Llama4TextConfig.from_dict(dict(base, num_hidden_layers=ns.layers,
                                           no_rope_layers=[i for i in range(ns.layers) if (i + 1) % 4 == 0]))
     pk, pk_kind = peaks()
-    if ns.preset in ("notedra", "zaposun", "latinex"):
+    if ns.preset in ("notedra", "zaposun", "latinex", "gisilix"):
+        import bench_gisilix
         import bench_latinex
         import bench_notedra
         import bench_zaposun
@@ -323,7 +325,8 @@ def main() -> int:
             ns.points = "8,64"
         if ns.steps == ap.get_default("steps"):
             ns.steps = 20
-        return {"notedra": bench_notedra, "zaposun": bench_zaposun, "latinex": bench_latinex}[ns.preset].run(ns, pk, pk_kind)
+        return {"notedra": bench_notedra, "zaposun": bench_zaposun, "latinex": bench_latinex,
+                "gisilix": bench_gisilix}[ns.preset].run(ns, pk, pk_kind)
     if ns.preset == "long":
         return long_context_run(ns, cfg, pk, pk_kind)
     dev = torch.device("cuda:0")

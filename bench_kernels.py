@@ -15,6 +15,8 @@
     python bench_kernels.py ssd --batch 64 --tokens 1              (state-space duality and its gated norm)
     python bench_kernels.py attention_keys_decode --batch 64 --context 8192     (keys-only pages)
     python bench_kernels.py attention_keys_prefill --tokens 2048 --mask window
+    python bench_kernels.py attention_prefill --tokens 2048 --softcap 30 --sinks        (capped scores, sinks)
+    python bench_kernels.py elementwise --op add_layernorm --tokens 2048 --hidden 2048
 
 Each run warms the kernel up, times ``--iters`` launches with CUDA events and prints one line with
 the time per launch and the achieved bytes or flops per second.  The inputs are larger than the L2
@@ -340,6 +342,33 @@ def elementwise(ns) -> None:
         def fn():
             x, delta = xs()
             ops.add_rmsnorm(x, delta, w, 1e-5, torch.bfloat16, want_fp32=ns.fp32_copy)
+    elif ns.op in ("add_layernorm", "add_dyt"):
+        copies = max(2, (300 << 20) // (T * H * 8) + 1)
+        xs = rotate([(torch.randn(T, H, device=DEV), torch.randn(T, H, device=DEV)) for _ in range(copies)])
+        w, b, alpha = torch.ones(H, device=DEV), torch.zeros(H, device=DEV), torch.full((1,), 0.5, device=DEV)
+        nbytes = T * H * (4 + 4 + 4 + 2 + (4 if ns.fp32_copy else 0))
+
+        def fn():
+            x, delta = xs()
+            if ns.op == "add_layernorm":
+                ops.add_layernorm(x, delta, w, b, 1e-5, torch.bfloat16, want_fp32=ns.fp32_copy)
+            else:
+                ops.add_dyt(x, delta, w, b, alpha, torch.bfloat16, want_fp32=ns.fp32_copy)
+    elif ns.op == "qkv_post_wide":      # norm over the whole q and k, query factor, q store, keys and values into pages
+        width = (nq + 2 * nkv) * d
+        copies = max(2, (300 << 20) // (T * width * 4) + 1)
+        qkvs = rotate([torch.randn(T, width, device=DEV) for _ in range(copies)])
+        pages = (T + ps - 1) // ps
+        kv = torch.zeros(pages, 2, nkv, ps, d, dtype=torch.bfloat16, device=DEV)
+        table = torch.arange(pages, dtype=torch.int32, device=DEV).view(1, pages)
+        positions = torch.arange(T, dtype=torch.int32, device=DEV)
+        row_req = torch.zeros(T, dtype=torch.int32, device=DEV)
+        wq, wk = torch.ones(nq * d, device=DEV), torch.ones(nkv * d, device=DEV)
+        q = torch.empty(T, nq, d, dtype=torch.bfloat16, device=DEV)
+        nbytes = T * width * 4 + T * width * 2
+        fn = lambda: ops.qkv_post_wide(qkvs(), positions, row_req, table, q, kv, nq=nq, nkv=nkv, d=d, page_size=ps,
+                                       q_weight=wq, k_weight=wk, eps=1e-6, q_count=nq * d, k_count=nkv * d, temp_coef=0.1,
+                                       temp_every=128.0, write_kv=True, has_kv=True)
     elif ns.op == "swiglu":
         copies = max(2, (300 << 20) // (T * 2 * I * 4) + 1)
         gus = rotate([torch.randn(T, 2 * I, device=DEV) for _ in range(copies)])
@@ -389,12 +418,14 @@ def attention_decode(ns) -> None:
     out = torch.empty(B, nq * d, dtype=torch.bfloat16, device=DEV)
     kind = {"full": ops.MASK_FULL, "chunk": ops.MASK_CHUNK, "window": ops.MASK_WINDOW}[ns.mask]
     keys = int((positions.long() + 1).sum())
+    sinks = torch.zeros(nq, device=DEV) if ns.sinks else None
     fn = lambda: ops.attention_decode(q, kv, table, row_req, positions, out, rows=None, num_rows=B, nq=nq, nkv=nkv, d=d,
                                       page_size=ps, mask_kind=kind, mask_span=ns.span, scale=1 / math.sqrt(d),
-                                      max_context=S, max_keys=keys)
+                                      max_context=S, max_keys=keys, softcap=ns.softcap, sinks=sinks)
     ms = _time(fn, ns.iters)
     nbytes = keys * nkv * d * 2 * 2
-    print(f"attention_decode batch={B} context={S}{'/' + str(ns.others_context) if ns.others_context else ''} heads={nq}/{nkv} d={d}: {ms * 1e3:.1f} us, {nbytes / ms / 1e6:.0f} GB/s")
+    print(f"attention_decode batch={B} context={S}{'/' + str(ns.others_context) if ns.others_context else ''} heads={nq}/{nkv} d={d} "
+          f"cap={ns.softcap} sinks={ns.sinks}: {ms * 1e3:.1f} us, {nbytes / ms / 1e6:.0f} GB/s")
 
 
 def attention_prefill(ns) -> None:
@@ -407,12 +438,13 @@ def attention_prefill(ns) -> None:
     out = torch.empty(T, nq * d, dtype=torch.bfloat16, device=DEV)
     kind = {"full": ops.MASK_FULL, "chunk": ops.MASK_CHUNK, "window": ops.MASK_WINDOW}[ns.mask]
     kernel = ops.attention_prefill if ns.warp_mma else ops.attention_prefill_tc
+    sinks = torch.zeros(nq, device=DEV) if ns.sinks else None
     fn = lambda: kernel(q, kv, table, tiles, out, nq=nq, nkv=nkv, d=d, page_size=ps, mask_kind=kind,
-                        mask_span=ns.span, scale=1 / math.sqrt(d))
+                        mask_span=ns.span, scale=1 / math.sqrt(d), softcap=ns.softcap, sinks=sinks)
     ms = _time(fn, ns.iters)
     pairs = sum(min(start + t + 1, (start + t) % ns.span + 1 if kind == ops.MASK_CHUNK else start + t + 1) for t in range(T))
     flops = 4 * nq * d * pairs
-    print(f"attention_prefill ({'m16n8k16' if ns.warp_mma else 'tcgen05'}) tokens={T} start={start} heads={nq}/{nkv} d={d}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.0f} TFLOP/s")
+    print(f"attention_prefill ({'m16n8k16' if ns.warp_mma else 'tcgen05'}) tokens={T} start={start} heads={nq}/{nkv} d={d} cap={ns.softcap} sinks={ns.sinks}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.0f} TFLOP/s")
 
 
 def ssd(ns) -> None:
@@ -521,7 +553,7 @@ def main(argv=None) -> int:
     p.add_argument("--impl", choices=["grouped", "rows", "library"], default="grouped")
     p.set_defaults(fn=dense)
     p = sub.add_parser("elementwise")
-    p.add_argument("--op", choices=["add_rmsnorm", "swiglu", "gather", "qkv_post"], default="add_rmsnorm")
+    p.add_argument("--op", choices=["add_rmsnorm", "swiglu", "gather", "qkv_post", "add_layernorm", "add_dyt", "qkv_post_wide"], default="add_rmsnorm")
     p.add_argument("--tokens", type=int, default=2048)
     p.add_argument("--hidden", type=int, default=5120)
     p.add_argument("--inter", type=int, default=8192)
@@ -586,6 +618,8 @@ def main(argv=None) -> int:
         p.add_argument("--mask", choices=["full", "chunk", "window"], default="full")
         p.add_argument("--span", type=int, default=8192)
         p.add_argument("--warp-mma", action="store_true", help="attention_prefill: the m16n8k16 kernel with 64-row tiles")
+        p.add_argument("--softcap", type=float, default=0.0, help="scores become softcap * tanh(score / softcap) (0: no cap)")
+        p.add_argument("--sinks", action="store_true", help="a sink per head in the softmax's denominator")
         p.set_defaults(fn=fn)
     p = sub.add_parser("ssd")
     p.add_argument("--batch", type=int, default=64)

@@ -25,7 +25,7 @@
 
 constexpr int ATT_THREADS = 128;
 constexpr int ATT_TILE = 128;
-constexpr int ATT_MAX_D = 512;
+constexpr int ATT_MAX_D = 1024;
 
 struct PagedAttnArgs {
     const void* q;           // [T, nq, d]

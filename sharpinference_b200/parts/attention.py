@@ -304,8 +304,8 @@ class PagedAttention(Mixer):
         if position is not None or value_position is not None or qk_norm is not None or values_are_keys:
             raise ValueError("the norm over the whole projection comes without position encoding, per-head norm or "
                              "values that are the keys")
-        if nq % nkv != 0 or min(dk, dv) <= 0 or max(dk, dv) > 512:
-            raise ValueError(f"heads ({nq}) must be a multiple of kv heads ({nkv}), head sizes ({dk}, {dv}) 1 .. 512")
+        if nq % nkv != 0 or min(dk, dv) <= 0 or max(dk, dv) > 1024:
+            raise ValueError(f"heads ({nq}) must be a multiple of kv heads ({nkv}), head sizes ({dk}, {dv}) 1 .. 1024")
         if keep_first and mask != "window":
             raise ValueError("kept first positions belong to the window mask")
         wq, wk, eps = wide_norm

@@ -92,9 +92,9 @@ class LatentAttention(Mixer):
         self.softmax_scale, self.act_dtype = float(softmax_scale), act_dtype
         # one cached row a token: [c | k_rot], padded to what the attention kernels take as a head size
         D = kv_rank + rot_dim
-        if D > 512:
+        if D > 1024:
             raise ValueError(f"kv_rank + rot_dim = {kv_rank + rot_dim} exceeds the largest head size of the attention "
-                             f"kernels (512)")
+                             f"kernels (1024; the tensor-core kernels take rows of up to 512, longer ones the general kernel)")
         D = (D + 15) // 16 * 16                   # a multiple of 16: the size the tensor-core kernels take
         self.head_dim = D
         self.cache_spec = CacheSpec(mask, span if mask != "full" else 0, 1, D, planes=1)

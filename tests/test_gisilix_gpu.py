@@ -536,6 +536,22 @@ def test_a_far_key_among_hundreds_carries_the_output(tmp_path, kind):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_latent_row_longer_than_the_tensor_core_kernels_take(tmp_path, dtype):
+    """A latent of 560 with 16 rotated elements: a cached row of 576 elements runs the general attention kernel in both
+    precisions, whole, in portions and token by token."""
+    from gisilix_models import lat2, top, write_config
+    cfg = top(40, 64, 1e-5, [lat2(2, 16, 16, 24, 560, 0.3, (16, 1000.0, (4.0, 64, 8.0, 1.0)), 90, None)])
+    folder = write_config(cfg, 0.1, 7, str(tmp_path))
+    cfg, w = plain.load_folder(folder)
+    reqs = {"a": traces.random_tokens(40, 150, seed=1), "b": traces.random_tokens(40, 70, seed=2)}
+    ref = {rid: plain.forward(cfg, w, toks) for rid, toks in reqs.items()}
+    for steps in (traces.whole(reqs), traces.mixed(reqs, max_live=2, tail=40)):
+        eng = engine_for(folder, dtype, traces.max_tokens(steps))
+        err, where = traces.worst_error(traces.replay(eng, steps), ref)
+        assert err < TOL[dtype], (err, where)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "C"])
 def test_long_decoding_through_graphs(folders, name, dtype):
     """Three requests decode 260 tokens each side by side, past every window's edge and over several pages;
