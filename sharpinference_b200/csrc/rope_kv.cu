@@ -461,6 +461,7 @@ SHARPI_API int sharpi_rotate_heads(const void* in, int in_dtype, const int* posi
 // numbers do not depend on the batch.  float32 throughout; q and the pages take the activation dtype.
 // ---------------------------------------------------------------------------------------
 constexpr int NORM_W_THREADS = 256;
+static_assert(NORM_W_THREADS == 256, "the two-sum reduction below lays eight warps' sums side by side");
 
 template <typename TO>
 __global__ void __launch_bounds__(NORM_W_THREADS)
@@ -479,13 +480,21 @@ qkv_post_wide_kernel(const float* qkv, int ld, const int* positions, const int* 
     for (int i = threadIdx.x; i < nQ; i += NORM_W_THREADS) sq += row[i] * row[i];
     if (store_kv)
         for (int i = threadIdx.x; i < nK; i += NORM_W_THREADS) sk += row[nQ + i] * row[nQ + i];
-    sq = block_sum(sq, scratch);
+    // both sums through one pass of the block's tree (a fixed order: the block size never changes)
+    {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        if (lane == 0) { scratch[warp] = sq; scratch[8 + warp] = sk; }
+        __syncthreads();
+        sq = warp_sum(lane < NORM_W_THREADS / 32 ? scratch[lane] : 0.0f);
+        sk = warp_sum(lane < NORM_W_THREADS / 32 ? scratch[8 + lane] : 0.0f);
+    }
     float fq = 1.0f / sqrtf(sq / (float)q_count + eps);
     if (temp_every > 0.0f) fq *= 1.0f + temp_coef * log1pf(floorf(((float)pos + 1.0f) / temp_every));
     TO* qo = q_out + (size_t)t * nQ;
     for (int i = threadIdx.x; i < nQ; i += NORM_W_THREADS) qo[i] = from_float<TO>(row[i] * fq * wq[i]);
     if (!store_kv) return;
-    sk = block_sum(sk, scratch);
     const float fk = 1.0f / sqrtf(sk / (float)k_count + eps);
     const int page = block_table[(size_t)row_req[t] * max_blocks + pos / page_size];
     if (page < 0) return;   // the host checks before the launch that every written position has a page

@@ -119,6 +119,57 @@ CASES = {"A": (CASE_A, 0.15, 41), "B": (CASE_B, 0.13, 42), "C": (CASE_C, 0.1, 43
          "E": (CASE_E, 0.1, 45)}
 
 
+def drawn_config(seed: int) -> dict:
+    """A configuration drawn from a seeded generator: three to nine layers in any order, widths of 64 to 320, grouped
+    and plain key heads of 16 to 128 elements with values of their own size, borrowing layers wherever an earlier
+    attention layer exists, latents of 32 to 512, windows from 17 to 600 or none, every kind of feed-forward."""
+    import random
+    r = random.Random(seed)
+    W = r.choice([64, 96, 128, 192, 256, 320])
+    layers, own = [], []
+
+    def mlp():
+        k = r.random()
+        if k < 0.15:
+            return None
+        if k < 0.5:
+            return dense(r.choice([48, 72, 128, 200]))
+        E = r.choice([2, 3, 5, 8, 12])
+        return moe(E, r.randint(1, min(E, 4)), r.choice([16, 24, 40, 64]), r.choice([0, 32, 64]))
+
+    def cap_and_temp():
+        return r.choice([0, 5.0, 20.0, 50.0]), r.choice([None, (0.3, r.choice([16, 128, 100]))])
+
+    for i in range(r.randint(3, 9)):
+        k = r.random()
+        if k < 0.4:
+            if own and r.random() < 0.4:
+                j = r.choice(own)
+                m = layers[j]["mixer"]
+                cap, temp = cap_and_temp()
+                layers.append(att(m["heads"], m["kv_heads"], m["dim"], m["vdim"], r.choice([0.1, 0.2, 0.3]), cap, temp, mlp(),
+                                  kv_from=j))
+            else:
+                G = r.choice([1, 2, 4])
+                d = r.choice([16, 32, 64, 64, 128, 40])
+                cap, temp = cap_and_temp()
+                layers.append(att(G * r.choice([1, 2, 3]), G, d, r.choice([d, d, 64, 32]), r.choice([0.1, 0.15, 0.2]), cap,
+                                  temp, mlp()))
+                own.append(i)
+        elif k < 0.7:
+            dr = r.choice([8, 16, 32, 64])
+            scaling = r.choice([None, (r.choice([2.0, 4.0, 8.0]), r.choice([64, 256, 2048]), r.choice([8.0, 32.0]),
+                                       r.choice([1.0, 2.0]))])
+            layers.append(lat2(r.choice([1, 2, 4, 6]), r.choice([16, 32, 64]), dr, r.choice([16, 32, 64]),
+                               r.choice([32, 64, 128, 100, 256]), r.choice([0.08, 0.12, 0.2]),
+                               (r.choice([dr, dr, dr // 2]), r.choice([1000.0, 50000.0]), scaling),
+                               r.choice([0, 17, 96, 256, 300, 600]), mlp()))
+        else:
+            layers.append(lat(r.choice([1, 2, 4, 8]), r.choice([16, 32, 64]), r.choice([16, 32, 64]),
+                              r.choice([32, 64, 128, 100, 512]), r.choice([0.1, 0.18]), mlp()))
+    return top(r.choice([100, 333, 1000]), W, r.choice([1e-6, 1e-5]), layers)
+
+
 def one_layer(name: str, index: int, mlp="same") -> dict:
     """A case's configuration cut down to one of its layers (``mlp``: the layer's own, or a replacement); a layer that
     borrows keys and values comes with the layer it borrows from, as layers 0 and 1."""

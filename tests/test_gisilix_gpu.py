@@ -535,6 +535,29 @@ def test_a_far_key_among_hundreds_carries_the_output(tmp_path, kind):
         eng.close_request("a")
 
 
+@pytest.mark.parametrize("seed", [3, 14, 15, 92, 65])
+def test_drawn_configurations(tmp_path, seed):
+    """Configurations drawn at random (layer order, sizes, windows, constants) with requests of 2 to 700 tokens: whole,
+    with decoded tails, and in drawn mixed batches, in 32-bit; bfloat16 whole, held to what rounding does."""
+    from gisilix_models import drawn_config, write_config
+    cfg = drawn_config(seed)
+    folder = write_config(cfg, 0.1, seed, str(tmp_path))
+    cfg, w = plain.load_folder(folder)
+    reqs = {f"q{i}": traces.random_tokens(cfg["vocab"], n, seed=seed * 7 + i) for i, n in enumerate([330, 37, 150, 700, 2])}
+    ref = {rid: plain.forward(cfg, w, toks) for rid, toks in reqs.items()}
+    for steps in (traces.whole(reqs), traces.tail_decode(reqs, tail=40), traces.drawn(reqs, seed=seed, max_live=4)):
+        eng = engine_for(folder, "float32", traces.max_tokens(steps))
+        err, where = traces.worst_error(traces.replay(eng, steps), ref)
+        eng.runner.flush_status()
+        assert err < TOL["float32"], (err, where)
+    steps = traces.whole(reqs)
+    eng = engine_for(folder, "bfloat16", traces.max_tokens(steps))
+    routing, slack = {}, {}
+    got = traces.replay(eng, steps, routing)
+    excess, where = worst_excess(got, reference_for(folder, reqs, routing, None, "bfloat16", slack), TOL["bfloat16"], slack)
+    assert excess < 2.0, (excess, where)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_a_latent_row_longer_than_the_tensor_core_kernels_take(tmp_path, dtype):
     """A latent of 560 with 16 rotated elements: a cached row of 576 elements runs the general attention kernel in both
