@@ -508,6 +508,101 @@ qkv_post_wide_kernel(const float* qkv, int ld, const int* positions, const int* 
     }
 }
 
+// The same with the row in registers: R pieces of four floats a thread, all loads issued before the first is used, so
+// the kernel is one trip to memory (a decode step is one block a row waiting for its loads).  Needs sizes that are
+// multiples of four (a piece lies within one head of q, k or v) and 16-byte aligned rows.  A thread adds its pieces'
+// squares in ascending order and the block's tree is fixed, so a row's numbers depend on the row alone; which of the
+// forms runs depends on the layer's sizes, never on the step.
+template <typename TO, int R>
+__global__ void __launch_bounds__(NORM_W_THREADS)
+qkv_post_wide_regs_kernel(const float* qkv, int ld, const int* positions, const int* row_req, const int* block_table,
+                          const float* __restrict__ wq, const float* __restrict__ wk, float eps, int q_count, int k_count,
+                          TO* q_out, TO* kv_base, int nq, int nkv, int d, int max_blocks, int page_size, float temp_coef,
+                          float temp_every, int write_kv, int has_kv) {
+    __shared__ float scratch[32];
+    pdl_wait();
+    const int t = blockIdx.x;
+    const float4* row = reinterpret_cast<const float4*>(qkv + (size_t)t * ld);
+    const int nQ = nq * d, nK = nkv * d;
+    const bool store_kv = has_kv && write_kv;
+    const int pieces = (store_kv ? nQ + 2 * nK : nQ) / 4;
+    float4 x[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int i = r * NORM_W_THREADS + threadIdx.x;
+        x[r] = i < pieces ? row[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const int pos = positions[t];
+    float sq = 0.0f, sk = 0.0f;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int e = 4 * (r * NORM_W_THREADS + threadIdx.x);
+        const float ss = x[r].x * x[r].x + x[r].y * x[r].y + x[r].z * x[r].z + x[r].w * x[r].w;
+        if (e < nQ) sq += ss;
+        else if (e < nQ + nK) sk += ss;
+    }
+    {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        if (lane == 0) { scratch[warp] = sq; scratch[8 + warp] = sk; }
+        __syncthreads();
+        sq = warp_sum(lane < NORM_W_THREADS / 32 ? scratch[lane] : 0.0f);
+        sk = warp_sum(lane < NORM_W_THREADS / 32 ? scratch[8 + lane] : 0.0f);
+    }
+    float fq = 1.0f / sqrtf(sq / (float)q_count + eps);
+    if (temp_every > 0.0f) fq *= 1.0f + temp_coef * log1pf(floorf(((float)pos + 1.0f) / temp_every));
+    const float fk = store_kv ? 1.0f / sqrtf(sk / (float)k_count + eps) : 0.0f;
+    int page = -1;
+    if (store_kv) page = block_table[(size_t)row_req[t] * max_blocks + pos / page_size];
+    const size_t plane = (size_t)nkv * page_size * d;
+    TO* kdst = kv_base + (page < 0 ? 0 : (size_t)page * 2 * plane + (size_t)(pos % page_size) * d);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int e = 4 * (r * NORM_W_THREADS + threadIdx.x);
+        if (e < nQ) {
+            const float4 w = *reinterpret_cast<const float4*>(wq + e);
+            store4<TO>(q_out + (size_t)t * nQ + e,
+                       make_float4(x[r].x * fq * w.x, x[r].y * fq * w.y, x[r].z * fq * w.z, x[r].w * fq * w.w));
+        } else if (page >= 0 && e < nQ + 2 * nK) {      // the host checks that every written position has a page
+            const bool is_k = e < nQ + nK;
+            const int i = e - nQ - (is_k ? 0 : nK);
+            const int head = i / d;
+            TO* dst = kdst + (is_k ? 0 : plane) + (size_t)head * page_size * d + (i - head * d);
+            if (is_k) {
+                const float4 w = *reinterpret_cast<const float4*>(wk + i);
+                store4<TO>(dst, make_float4(x[r].x * fk * w.x, x[r].y * fk * w.y, x[r].z * fk * w.z, x[r].w * fk * w.w));
+            } else {
+                store4<TO>(dst, x[r]);
+            }
+        }
+    }
+}
+
+template <typename TO>
+static int launch_wide(const float* qkv, int ld, const int* positions, const int* row_req, const int* block_table,
+                       const float* wq, const float* wk, float eps, int q_count, int k_count, TO* q_out, TO* kv_base, int T,
+                       int nq, int nkv, int d, int max_blocks, int page_size, float temp_coef, float temp_every,
+                       int write_kv, int has_kv, cudaStream_t stream) {
+    const int floats = (has_kv && write_kv) ? (nq + 2 * nkv) * d : nq * d;
+    const uintptr_t ptrs = reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
+                           reinterpret_cast<uintptr_t>(kv_base) | reinterpret_cast<uintptr_t>(wq) |
+                           reinterpret_cast<uintptr_t>(wk);
+    const bool pieces = d % 4 == 0 && ld % 4 == 0 && (ptrs & 15) == 0 && floats <= 8 * 4 * NORM_W_THREADS;
+#define WIDE_ARGS qkv, ld, positions, row_req, block_table, wq, wk, eps, q_count, k_count, q_out, kv_base, nq, nkv, d, \
+                  max_blocks, page_size, temp_coef, temp_every, write_kv, has_kv
+    if (pieces && floats <= 2 * 4 * NORM_W_THREADS)
+        SHARPI_LAUNCH_PDL((qkv_post_wide_regs_kernel<TO, 2>), T, NORM_W_THREADS, 0, stream, WIDE_ARGS);
+    else if (pieces && floats <= 4 * 4 * NORM_W_THREADS)
+        SHARPI_LAUNCH_PDL((qkv_post_wide_regs_kernel<TO, 4>), T, NORM_W_THREADS, 0, stream, WIDE_ARGS);
+    else if (pieces)
+        SHARPI_LAUNCH_PDL((qkv_post_wide_regs_kernel<TO, 8>), T, NORM_W_THREADS, 0, stream, WIDE_ARGS);
+    else
+        SHARPI_LAUNCH_PDL(qkv_post_wide_kernel<TO>, T, NORM_W_THREADS, 0, stream, WIDE_ARGS);
+#undef WIDE_ARGS
+    return SHARPI_OK;
+}
+
 SHARPI_API int sharpi_qkv_post_wide(const float* qkv, int ld, const int* positions, const int* row_req,
                                     const int* block_table, const float* wq, const float* wk, float eps, int q_count,
                                     int k_count, void* q_out, void* kv_base, int out_dtype, int T, int nq, int nkv,
@@ -518,14 +613,12 @@ SHARPI_API int sharpi_qkv_post_wide(const float* qkv, int ld, const int* positio
     if (has_kv && (!wk || k_count <= 0 || ld < (nq + 2 * nkv) * d)) return SHARPI_BAD_ARGUMENT;
     if (ld < nq * d) return SHARPI_BAD_ARGUMENT;
     if (out_dtype == SHARPI_F32)
-        SHARPI_LAUNCH_PDL(qkv_post_wide_kernel<float>, T, NORM_W_THREADS, 0, stream, qkv, ld, positions, row_req,
-                          block_table, wq, wk, eps, q_count, k_count, (float*)q_out, (float*)kv_base, nq, nkv, d,
-                          max_blocks, page_size, temp_coef, temp_every, write_kv, has_kv);
-    else if (out_dtype == SHARPI_BF16)
-        SHARPI_LAUNCH_PDL(qkv_post_wide_kernel<bf16>, T, NORM_W_THREADS, 0, stream, qkv, ld, positions, row_req,
-                          block_table, wq, wk, eps, q_count, k_count, (bf16*)q_out, (bf16*)kv_base, nq, nkv, d,
-                          max_blocks, page_size, temp_coef, temp_every, write_kv, has_kv);
-    else
-        return SHARPI_BAD_ARGUMENT;
-    return SHARPI_OK;
+        return launch_wide<float>(qkv, ld, positions, row_req, block_table, wq, wk, eps, q_count, k_count, (float*)q_out,
+                                  (float*)kv_base, T, nq, nkv, d, max_blocks, page_size, temp_coef, temp_every, write_kv,
+                                  has_kv, stream);
+    if (out_dtype == SHARPI_BF16)
+        return launch_wide<bf16>(qkv, ld, positions, row_req, block_table, wq, wk, eps, q_count, k_count, (bf16*)q_out,
+                                 (bf16*)kv_base, T, nq, nkv, d, max_blocks, page_size, temp_coef, temp_every, write_kv,
+                                 has_kv, stream);
+    return SHARPI_BAD_ARGUMENT;
 }

@@ -224,18 +224,22 @@ def test_a_sink_far_above_every_score_empties_the_row():
         assert float((o[:, 1] - b[:, 1]).abs().max()) < 2e-2, run
 
 
-@pytest.mark.parametrize("nq,nkv,d,count_d,page,borrow", [(4, 2, 16, 16, 16, False), (3, 3, 10, 10, 4, False),
-                                                          (2, 1, 32, 24, 8, False), (4, 1, 64, 64, 64, True)])
-def test_norm_over_the_whole_projection_and_cache_write(nq, nkv, d, count_d, page, borrow):
+@pytest.mark.parametrize("nq,nkv,d,count_d,page,borrow,pad", [
+    (4, 2, 16, 16, 16, False, 5), (4, 2, 16, 16, 16, False, 8), (3, 3, 10, 10, 4, False, 5), (2, 1, 32, 24, 8, False, 4),
+    (4, 1, 64, 64, 64, True, 5), (4, 1, 64, 64, 64, True, 12), (16, 4, 128, 128, 64, False, 8), (32, 8, 128, 128, 16, False, 0),
+    (72, 8, 128, 128, 64, False, 4)])
+def test_norm_over_the_whole_projection_and_cache_write(nq, nkv, d, count_d, page, borrow, pad):
     """q and k as wholes are divided by their root mean square (the mean over ``count_d`` elements a head where heads
-    are padded), weighted, q is multiplied by the position's factor, and k and v land in the rows' pages."""
+    are padded), weighted, q is multiplied by the position's factor, and k and v land in the rows' pages.  Rows that
+    are 16-byte aligned take the form of the kernel that holds the row in registers (2, 4 or 8 pieces a thread), the
+    others and rows beyond 8192 floats the one that reads the row twice."""
     from sharpinference_b200.kernels import ops
     T, eps, coef, every = 40, 1e-5, 0.4, 7.0
     width = nq * d + (0 if borrow else 2 * nkv * d)
     core = _rand(T, width, seed=d, scale=2.0).float()
     if count_d < d:                                                             # padded heads hold zeros
         core.view(T, -1, d)[:, :, count_d:] = 0
-    qkv = torch.cat([core, _rand(T, 5, seed=9).float()], dim=1)                 # a column range of a wider product
+    qkv = torch.cat([core, _rand(T, pad, seed=9).float()], dim=1)               # a column range of a wider product
     wq, wk = _rand(nq * d, seed=1).float(), _rand(nkv * d, seed=2).float()
     pos = torch.tensor([(3 * t) % 37 for t in range(T)], dtype=torch.int32)
     reqs = torch.tensor([t % 2 for t in range(T)], dtype=torch.int32)
